@@ -5,8 +5,9 @@ from .spec import ArchitectureSpec, LayerSpec, PartSpec, RunEntry
 from .llama import LlamaConfig, RopeScaling
 from .dedutar import DedutarConfig
 from .monolix import MonolixConfig
+from .bazurax import BazuraxConfig
 
 __all__ = [
-    "ArchitectureSpec", "ConfigError", "DedutarConfig", "LayerSpec", "LlamaConfig", "MonolixConfig", "PartSpec", "RopeScaling", "RunEntry",
+    "ArchitectureSpec", "BazuraxConfig", "ConfigError", "DedutarConfig", "LayerSpec", "LlamaConfig", "MonolixConfig", "PartSpec", "RopeScaling", "RunEntry",
     "config_class_for", "config_from_dict", "load_config", "register_architecture", "registered_architectures",
 ]

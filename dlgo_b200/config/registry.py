@@ -51,13 +51,26 @@ def config_class_for(name: str) -> Any:
         ) from None
 
 
-def config_from_dict(d: Mapping[str, Any]) -> ArchitectureConfig:
+def config_from_dict(d: Mapping[str, Any], model_dir: str | None = None) -> ArchitectureConfig:
+    """The typed configuration of ``d``.  A class whose design leaves a size to the weight file (``shapes_from_file``
+    True) also gets the file's tensor shapes, name -> shape, when a model folder is at hand."""
     archs = d.get("architectures", d.get("architecture"))      # a list of names, or one name under either key
     if isinstance(archs, str):
         archs = [archs]
     if not archs or not isinstance(archs, (list, tuple)):
         raise ConfigError('config.json has no "architectures" (or "architecture") entry')
     cls = config_class_for(str(archs[0]))
+    if getattr(cls, "shapes_from_file", False) and model_dir is not None:
+        from ..weights.safetensors_io import Checkpoint, SafetensorsError
+        try:
+            ck = Checkpoint(model_dir)
+        except (OSError, SafetensorsError):
+            return cls.from_dict(d)        # no readable weight file: the class says what it misses
+        try:
+            shapes = {n: tuple(ck.info(n).shape) for n in ck.names()}
+        finally:
+            ck.close()
+        return cls.from_dict(d, shapes=shapes)
     return cls.from_dict(d)
 
 
@@ -72,4 +85,4 @@ def load_config(model_dir: str) -> ArchitectureConfig:
         raise ConfigError(f"{path}: not valid JSON ({e})") from None
     if not isinstance(d, dict):
         raise ConfigError(f"{path}: top level must be an object")
-    return config_from_dict(d)
+    return config_from_dict(d, model_dir)

@@ -46,6 +46,9 @@ LIBRARIES: Dict[str, List[str]] = {
     "postnorm": ["postnorm.cu"],
     "moe": ["moe.cu"],
     "moe_tc": ["moe_tc.cu"],
+    "layernorm": ["layernorm.cu"],
+    "timemix": ["timemix.cu"],
+    "wholenorm_append": ["wholenorm_append.cu"],
 }
 _HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "attention_decode_tiles.cuh", "tcgen05.cuh"]
 

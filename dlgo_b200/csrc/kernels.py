@@ -175,6 +175,8 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.T
 # ----------------------------------------------- residual streams and their norms
 NORM_NONE, NORM_RMS, NORM_DYT = 0, 1, 2
 ACT_NONE, ACT_RELU2, ACT_SILU, ACT_GELU_TANH = 0, 1, 2, 3
+ACT_TANH = 4           # (the elementwise bias_act only)
+GATE_SIGMOID, GATE_SILU = 0, 1
 MAX_STREAMS = 8
 
 
@@ -250,18 +252,26 @@ def bias_act(z: torch.Tensor, bias: Optional[torch.Tensor], act: int, out_dtype:
     return out
 
 
-def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
-    """``rms(o) * w * sigmoid(gate)`` row by row; o and gate are fp32 [T, n] views with unit inner stride."""
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                  group: Optional[int] = None, gate_act: int = GATE_SIGMOID, scale: float = 1.0) -> torch.Tensor:
+    """``rms(o) * w * g(gate) * scale`` row by row; o and gate are fp32 [T, n] views with unit inner stride.
+    ``group``: the mean square is taken over each run of ``group`` neighbours (a head) on its own instead of the
+    whole row; ``w`` None: no weight; ``gate_act``: sigmoid or silu of the gate."""
     for n_, t in (("o", o), ("gate", gate)):
         if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
             raise KernelError(f"gated_rmsnorm: {n_} must be 2-D float32 with unit inner stride")
-    _need(w, torch.float32, "w")
     T, n = o.shape
-    if tuple(gate.shape) != (T, n) or w.numel() != n:
+    if w is not None:
+        _need(w, torch.float32, "w")
+    if tuple(gate.shape) != (T, n) or (w is not None and w.numel() != n):
         raise KernelError("gated_rmsnorm: shapes differ")
+    group = n if group is None else int(group)
+    if group <= 0 or n % group:
+        raise KernelError(f"gated_rmsnorm: rows of {n} do not split into groups of {group}")
     out = torch.empty((T, n), dtype=out_dtype, device=o.device)
     st = _lib("streams").dlgo_gated_rmsnorm(_ptr(o), _i(o.stride(0)), _ptr(gate), _i(gate.stride(0)), _ptr(w), _ptr(out),
-                                            _i(dtype_code(out_dtype)), _i(T), _i(n), _f(eps), _stream())
+                                            _i(dtype_code(out_dtype)), _i(T), _i(n), _f(eps), _i(group), _i(gate_act),
+                                            _f(scale), _stream())
     _check(st, "gated_rmsnorm")
     return out
 
@@ -411,10 +421,10 @@ def attention_prefill_tc_rows(q: torch.Tensor, kv: torch.Tensor, k_col: int, v_c
 # ---------------------------------------------------------- lightning attention
 def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, tiles: torch.Tensor, n_seqs: int,
                    seq_slot: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, num_heads: int, qk_dim: int,
-                   v_dim: int) -> torch.Tensor:
+                   v_dim: int, silu: bool = True) -> torch.Tensor:
     """Decayed linear attention of packed tokens, sequence by sequence in token order, continuing each
     sequence's fp32 state ``state`` [slots, H, qk_dim, v_dim] (in place).  ``proj`` [T, ld] fp32 holds the
-    q, k and v projections at the given column offsets (silu is applied here); ``tiles`` [n_seqs, 3] lists
+    q, k and v projections at the given column offsets (with ``silu``, silu is applied here); ``tiles`` [n_seqs, 3] lists
     (sequence, first packed token, count).  Returns fp32 [T, H*v_dim]."""
     if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
         raise KernelError("lightning_scan: proj must be 2-D float32 with unit inner stride")
@@ -429,7 +439,7 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, tiles
     st = _lib("lightning").dlgo_lightning_scan(_ptr(proj), _i(proj.stride(0)), _i(q_off), _i(k_off), _i(v_off),
                                                _ptr(tiles), _i(n_seqs), _ptr(seq_slot), _ptr(decay), _ptr(state),
                                                _ptr(out), _i(out.stride(0)), _i(num_heads), _i(qk_dim), _i(v_dim),
-                                               _stream())
+                                               _i(1 if silu else 0), _stream())
     _check(st, "lightning_scan")
     return out
 
@@ -441,7 +451,8 @@ def lightning_segments_takes(qk_dim: int) -> bool:
 
 def lightning_segments(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, tiles: torch.Tensor, n_tiles: int,
                        direct: bool, seq_slot: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
-                       scratch: Optional[torch.Tensor], num_heads: int, qk_dim: int, v_dim: int) -> torch.Tensor:
+                       scratch: Optional[torch.Tensor], num_heads: int, qk_dim: int, v_dim: int,
+                       silu: bool = True) -> torch.Tensor:
     """:func:`lightning_scan` with every sequence's tokens cut into consecutive segments (``tiles`` [n_tiles, 3],
     a sequence's segments in token order) that run side by side: each first computes its own end state from
     zero, then starts from the decayed sum of what lies before it.  ``direct``: one segment per sequence (no
@@ -463,9 +474,207 @@ def lightning_segments(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, t
     st = _lib("lightning").dlgo_lightning_segments(
         _ptr(proj), _i(proj.stride(0)), _i(q_off), _i(k_off), _i(v_off), _ptr(tiles), _i(n_tiles),
         _i(1 if direct else 0), _ptr(seq_slot), _ptr(decay), _ptr(state), _ptr(scratch), _ptr(out), _i(out.stride(0)),
-        _i(num_heads), _i(qk_dim), _i(v_dim), _stream())
+        _i(num_heads), _i(qk_dim), _i(v_dim), _i(1 if silu else 0), _stream())
     _check(st, "lightning_segments", 1 if direct else 2)
     return out
+
+
+def rotate_scale(proj: torch.Tensor, q_off: int, k_off: int, freq: Optional[torch.Tensor], rot: int,
+                 token_pos: torch.Tensor, num_heads: int, qk_dim: int, k_scale: float) -> None:
+    """In place on the fp32 projection rows ``proj`` [T, ld]: the first ``rot`` numbers of every q and k head
+    (``num_heads`` heads of ``qk_dim`` at the column offsets) turn in pairs (i, i + rot/2) by the angle
+    ``float(position) * freq[i]``; keys are then multiplied by ``k_scale``."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("rotate_scale: proj must be 2-D float32 with unit inner stride")
+    _need(token_pos, torch.int32, "token_pos")
+    if rot:
+        _need(freq, torch.float32, "freq")
+        if freq.numel() != rot // 2:
+            raise KernelError("rotate_scale: one frequency per rotated pair")
+    hi = max(q_off, k_off) + num_heads * qk_dim
+    if hi > proj.shape[1] or abs(q_off - k_off) < num_heads * qk_dim:
+        raise KernelError("rotate_scale: q and k columns must lie inside the rows and apart")
+    st = _lib("lightning").dlgo_rotate_scale(_ptr(proj), _i(proj.stride(0)), _i(q_off), _i(k_off),
+                                             _ptr(freq if rot else None), _i(rot), _ptr(token_pos), _i(proj.shape[0]),
+                                             _i(num_heads), _i(qk_dim), _f(k_scale), _stream())
+    _check(st, "rotate_scale")
+
+
+# ------------------------------------------------------------------ time mixing
+def token_shift_mix(x: torch.Tensor, mu: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
+                    state: torch.Tensor, prev_off: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Blends of every token's input with the previous token's: ``out[s, t] = x[t] + (x[t-1] - x[t]) * mu[s]`` for the
+    fp32 rows ``x`` [T, d] and ``mu`` [n, d]; a sequence's first token of the step reads its predecessor from the
+    sequence's row of ``state`` [slots, row] (fp32) at column ``prev_off``.  Returns [n, T, d] in ``out_dtype``."""
+    _need(x, torch.float32, "x")
+    _need(mu, torch.float32, "mu")
+    _need(token_seq, torch.int32, "token_seq")
+    _need(seq_slot, torch.int32, "seq_slot")
+    T, d = x.shape
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or prev_off + d > state.shape[1]:
+        raise KernelError("token_shift_mix: state must be 2-D float32 rows that hold d numbers at prev_off")
+    if mu.dim() != 2 or mu.shape[1] != d:
+        raise KernelError("token_shift_mix: mu must be [n, d]")
+    out = torch.empty((mu.shape[0], T, d), dtype=out_dtype, device=x.device)
+    st = _lib("timemix").dlgo_token_shift_mix(_ptr(x), _ptr(mu), _i(mu.shape[0]), _ptr(token_seq), _ptr(seq_slot),
+                                              _ptr(state), _ll(state.stride(0)), _i(prev_off), _ptr(out),
+                                              _i(dtype_code(out_dtype)), _i(T), _i(d), _stream())
+    _check(st, "token_shift_mix")
+    return out
+
+
+def wkv_segments_takes(head_dim: int) -> bool:
+    """Whether the segment kernels (the state's columns in registers, segments side by side) take this head size."""
+    return head_dim in (32, 64, 128)
+
+
+def wkv_scratch_floats(n_tiles: int, num_heads: int, head_dim: int) -> int:
+    return n_tiles * num_heads * (2 * head_dim * head_dim + head_dim)
+
+
+def wkv(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zw: torch.Tensor, w0: torch.Tensor, u: torch.Tensor,
+        tiles: torch.Tensor, n_tiles: int, direct: bool, segments: bool, seq_slot: torch.Tensor, state: torch.Tensor,
+        x: Optional[torch.Tensor], scratch: Optional[torch.Tensor], num_heads: int, head_dim: int) -> torch.Tensor:
+    """The recurrence with a per-token, per-channel decay ``w = exp(-exp(zw + w0))`` and the bonus ``u`` for the
+    current token, over packed tokens, continuing each sequence's state.  r, k, v, zw: fp32 [T, H * n]
+    (contiguous); w0, u: fp32 [H * n]; ``state`` [slots, row] fp32 rows of H * n * n state numbers followed, when
+    ``x`` (fp32 [T, d]) is given, by the d numbers of the sequence's last input, which is stored there.
+    ``segments``: ``tiles`` cuts sequences into segments that run side by side (head sizes 32 / 64 / 128; unless
+    ``direct``, with ``scratch`` of :func:`wkv_scratch_floats`); else one row of ``tiles`` per sequence, any head
+    size.  Returns fp32 [T, H * n]."""
+    T = r.shape[0]
+    ld = num_heads * head_dim
+    for n_, t in (("r", r), ("k", k), ("v", v), ("zw", zw)):
+        _need(t, torch.float32, n_)
+        if tuple(t.shape) != (T, ld):
+            raise KernelError(f"wkv: {n_} must be [{T}, {ld}]")
+    for n_, t in (("w0", w0), ("u", u)):
+        _need(t, torch.float32, n_)
+        if t.numel() != ld:
+            raise KernelError(f"wkv: {n_} must hold one number per head and channel")
+    _need(tiles, torch.int32, "tiles")
+    _need(seq_slot, torch.int32, "seq_slot")
+    d = 0
+    if x is not None:
+        _need(x, torch.float32, "x")
+        d = x.shape[1]
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or \
+            state.shape[1] < ld * head_dim + d:
+        raise KernelError("wkv: state must be 2-D float32 rows of heads * n * n (+ d) numbers")
+    out = torch.empty((T, ld), dtype=torch.float32, device=r.device)
+    lib = _lib("timemix")
+    if segments:
+        if not direct:
+            need = wkv_scratch_floats(n_tiles, num_heads, head_dim)
+            if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+                raise KernelError(f"wkv: {n_tiles} segments need {need} floats of scratch")
+        st = lib.dlgo_wkv_segments(_ptr(r), _ptr(k), _ptr(v), _ptr(zw), _i(ld), _ptr(w0), _ptr(u), _ptr(tiles),
+                                   _i(n_tiles), _i(1 if direct else 0), _ptr(seq_slot), _ptr(state),
+                                   _ll(state.stride(0)), _ptr(x), _i(d), _ptr(scratch), _ptr(out), _i(num_heads),
+                                   _i(head_dim), _stream())
+        _check(st, "wkv_segments", 1 if direct else 2)
+    else:
+        st = lib.dlgo_wkv_scan(_ptr(r), _ptr(k), _ptr(v), _ptr(zw), _i(ld), _ptr(w0), _ptr(u), _ptr(tiles), _i(n_tiles),
+                               _ptr(seq_slot), _ptr(state), _ll(state.stride(0)), _ptr(x), _i(d), _ptr(out),
+                               _i(num_heads), _i(head_dim), _stream())
+        _check(st, "wkv_scan")
+    return out
+
+
+# ------------------------------------------------------ layer norm, norm of a sublayer's result
+NORMED_LAYER, NORMED_RMS = 0, 1
+
+
+def layernorm_rows(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                   rows: Optional[torch.Tensor] = None, kind: int = NORMED_LAYER, in_place: bool = False) -> torch.Tensor:
+    """``(x - mean) / sqrt(var + eps) * w`` (or, ``kind`` NORMED_RMS, ``x / sqrt(mean(x^2) + eps) * w``) of the fp32
+    rows ``x`` [T, d], or of the rows listed in ``rows`` (int32), in ``out_dtype``; ``in_place``: x is rewritten."""
+    _need(x, torch.float32, "x")
+    _need(w, torch.float32, "w")
+    T, d = x.shape
+    if w.numel() != d:
+        raise KernelError("layernorm_rows: one weight per channel")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    R = T if rows is None else rows.numel()
+    if in_place:
+        if rows is not None or out_dtype != torch.float32:
+            raise KernelError("layernorm_rows: in place only for all rows in float32")
+        out = x
+    else:
+        out = torch.empty((R, d), dtype=out_dtype, device=x.device)
+    st = _lib("layernorm").dlgo_layernorm_rows(_ptr(x), _ptr(w), _ptr(out), _i(dtype_code(out_dtype)), _ptr(rows), _i(R),
+                                               _i(d), _i(kind), _f(eps), _stream())
+    _check(st, "layernorm_rows")
+    return out
+
+
+def add_normed(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, act_dtype: Optional[torch.dtype],
+               kind: int = NORMED_LAYER, clear_y: bool = True) -> Optional[torch.Tensor]:
+    """``x <- x + norm(y) * w`` on the fp32 residual stream ``x`` [T, d], in place (``y`` fp32 [T, d], left zero with
+    ``clear_y``); returns the new rows in ``act_dtype`` (None: no copy)."""
+    _need(x, torch.float32, "x")
+    _need(y, torch.float32, "y")
+    _need(w, torch.float32, "w")
+    T, d = x.shape
+    if tuple(y.shape) != (T, d) or w.numel() != d:
+        raise KernelError("add_normed: y must have x's shape and w one element per channel")
+    act = None if act_dtype is None else torch.empty((T, d), dtype=act_dtype, device=x.device)
+    st = _lib("layernorm").dlgo_add_normed(_ptr(x), _ptr(y), _ptr(w), _ptr(act),
+                                           _i(dtype_code(act_dtype or torch.float32)), _i(T), _i(d), _i(kind), _f(eps),
+                                           _i(1 if clear_y else 0), _stream())
+    _check(st, "add_normed")
+    return act
+
+
+# --------------------------------------- queries and keys normed as a whole, cache append, head gates
+def wholenorm_append(proj: torch.Tensor, w_q: Optional[torch.Tensor], w_k: Optional[torch.Tensor], eps: float,
+                     token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
+                     page_table: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, num_heads: int,
+                     num_kv_heads: int, qk_dim: int, v_dim: int, has_gate: bool, gate_scale: float, write_cache: bool,
+                     clear: bool, out_dtype: torch.dtype):
+    """From the fp32 rows ``proj`` [T, >= Hq qk + Hkv (qk + v) (+ Hq)]: queries and keys each divided by the root mean
+    square over ALL their numbers and multiplied by ``w_q`` / ``w_k`` (None: left as they are); keys and values
+    appended to their pages ``[pages, kv_heads, page_size, hd]`` with zeros behind a head's own numbers; returns
+    (queries [T, Hq * hd] in ``out_dtype``, gates [T, Hq] fp32 = sigmoid(logit) * gate_scale, or None)."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("wholenorm_append: proj must be 2-D float32 with unit inner stride")
+    for n_, t in (("w_q", w_q), ("w_k", w_k)):
+        if t is not None:
+            _need(t, torch.float32, n_)
+    if (w_q is not None and w_q.numel() != num_heads * qk_dim) or (w_k is not None and w_k.numel() != num_kv_heads * qk_dim):
+        raise KernelError("wholenorm_append: the norm weights must cover the whole projections")
+    for n_, t in (("token_pos", token_pos), ("token_seq", token_seq), ("seq_slot", seq_slot), ("page_table", page_table)):
+        _need(t, torch.int32, n_)
+    _need(kpages, out_dtype, "kpages")
+    _need(vpages, out_dtype, "vpages")
+    P, hkv, ps, hd = kpages.shape
+    if hkv != num_kv_heads or tuple(vpages.shape) != tuple(kpages.shape):
+        raise KernelError("wholenorm_append: pages must be [pages, kv_heads, page_size, hd], keys and values alike")
+    T = proj.shape[0]
+    q = torch.empty((T, num_heads * hd), dtype=out_dtype, device=proj.device)
+    gate = torch.empty((T, num_heads), dtype=torch.float32, device=proj.device) if has_gate else None
+    st = _lib("wholenorm_append").dlgo_wholenorm_append(
+        _ptr(proj), _i(proj.stride(0)), _ptr(w_q), _ptr(w_k), _f(eps), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot),
+        _ptr(page_table), _i(page_table.shape[1]), _ptr(kpages), _ptr(vpages), _ptr(q), _ptr(gate),
+        _i(dtype_code(out_dtype)), _i(T), _i(num_heads), _i(num_kv_heads), _i(qk_dim), _i(v_dim), _i(hd), _i(ps),
+        _i(1 if has_gate else 0), _f(gate_scale), _i(1 if write_cache else 0), _i(1 if clear else 0), _stream())
+    _check(st, "wholenorm_append")
+    return q, gate
+
+
+def scale_heads(a: torch.Tensor, gate: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """``a[t, h, :] *= gate[t, h]`` in place for ``a`` [T, H * head_dim] (float32 or bfloat16) and fp32 ``gate`` [T, H]."""
+    _need(a, None, "a")
+    _need(gate, torch.float32, "gate")
+    T, n = a.shape
+    H = gate.shape[1]
+    if n != H * head_dim or gate.shape[0] != T:
+        raise KernelError("scale_heads: a must be [T, H * head_dim] and gate [T, H]")
+    st = _lib("wholenorm_append").dlgo_scale_heads(_ptr(a), _ptr(gate), _i(dtype_code(a.dtype)), _i(T), _i(H),
+                                                   _i(head_dim), _stream())
+    _check(st, "scale_heads")
+    return a
 
 
 # ------------------------------------------------------------------------ GEMM
@@ -602,7 +811,7 @@ MOE_FEW_ROWS, MOE_TILE_ROWS, MOE_TC_ROWS, MOE_TC_PAIR_ROWS = 8, 64, 128, 256    
 
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], n_outputs: int,
                has_gate: bool, top: int, groups: int, keep: int, sigmoid_scores: bool = False,
-               renormalize: bool = False, plan: Optional[tuple] = None):
+               renormalize: bool = False, plan: Optional[tuple] = None, logit_bias: Optional[torch.Tensor] = None):
     """Router of a mixture of experts for ``h`` [T, d]: returns (chosen outputs [T, top] int32, their weights
     [T, top] fp32, gate [T] fp32 or None, plan).  ``w_router`` is fp32 [n_outputs (+ 1 gate row), d].
     ``plan`` = (experts that hold tensors, rows per tile): the :class:`MoEPlan` of :func:`moe_plan` is made as well,
@@ -618,6 +827,10 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[tor
         _need(correction, torch.float32, "correction")
         if correction.numel() != n_outputs:
             raise KernelError("moe_router: one correction per router output")
+    if logit_bias is not None:
+        _need(logit_bias, torch.float32, "logit_bias")
+        if logit_bias.numel() != n_outputs:
+            raise KernelError("moe_router: one logit bias per router output")
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     wt = torch.empty((T, top), dtype=torch.float32, device=h.device)
     gate = torch.empty((T,), dtype=torch.float32, device=h.device) if has_gate else None
@@ -625,7 +838,7 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[tor
     p = _empty_plan(T * top, plan[0], plan[1], h.device) if plan is not None and plan[0] > 0 else None
     fused = ctypes.c_int(0)
     st = _lib("moe").dlgo_moe_router(
-        _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(w_router), _ptr(correction), _ptr(z), _ptr(idx),
+        _ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(w_router), _ptr(correction), _ptr(logit_bias), _ptr(z), _ptr(idx),
         _ptr(wt), _ptr(gate), _i(T), _i(d), _i(n_outputs), _i(1 if has_gate else 0), _i(top), _i(groups), _i(keep),
         _i(1 if sigmoid_scores else 0), _i(1 if renormalize else 0), _i(plan[0] if p is not None else 0),
         _i(plan[1] if p is not None else 0), _ptr(p.offsets if p is not None else None),
@@ -1102,7 +1315,8 @@ def check_device_errors() -> None:
                               "invalid and its counters must be zeroed again (build a new engine)")
         if v != 0:
             raise KernelError("a token's position had no page in the cache's table (persistent decode kernel)")
-    for lib, fn in (("rope_append", "dlgo_rope_append_error"), ("headnorm_rope", "dlgo_headnorm_rope_error")):
+    for lib, fn in (("rope_append", "dlgo_rope_append_error"), ("headnorm_rope", "dlgo_headnorm_rope_error"),
+                    ("wholenorm_append", "dlgo_wholenorm_append_error")):
         if lib in build._loaded and getattr(build._loaded[lib], fn)() != 0:
             raise KernelError("a token's position had no page in the cache's table: its keys and values were not "
                               "stored and the step's results are invalid")

@@ -1,13 +1,14 @@
 // Linear attention with a per-head decay ("lightning attention"), as a recurrence over a fixed-size state.
 //
-// Per head, with q_t = silu(Wq h_t), k_t = silu(Wk h_t) (dk numbers) and v_t = silu(Wv h_t) (dv numbers):
+// Per head, with q_t = a(Wq h_t), k_t = a(Wk h_t) (dk numbers) and v_t = a(Wv h_t) (dv numbers), where a is silu
+// (`act` 1) or nothing (`act` 0: the caller has prepared q and k, e.g. rotated and scaled them):
 //   S_t = lambda * S_(t-1) + k_t v_t^T          S is [dk, dv], fp32, zero at a sequence's start
 //   o_t = S_t^T q_t
 // The state of a sequence lives in its slot of the state area between steps, so a prompt may arrive in any
 // number of portions and decoding continues where the prompt stopped.
 //
 // lightning_scan: one block per (sequence, head, run of value columns); its part of the state sits in shared
-// memory while the block walks the sequence's tokens of this step in order.  The projections arrive as fp32 rows [q | k | v | ...]; silu,
+// memory while the block walks the sequence's tokens of this step in order.  The projections arrive as fp32 rows [q | k | v | ...]; activation,
 // decay, state and output are fp32.
 #include "common.cuh"
 
@@ -18,7 +19,7 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 __global__ void lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                                       const int* __restrict__ tiles, const int* __restrict__ seq_slot,
                                       const float* __restrict__ decay, float* __restrict__ state,
-                                      float* __restrict__ out, int ldo, int H, int dk, int dv, int dvc) {
+                                      float* __restrict__ out, int ldo, int H, int dk, int dv, int dvc, int act) {
   pdl_launch_dependents();
   extern __shared__ float smem[];
   // the block's columns [e0, e0 + n) of the state (columns are independent of one another)
@@ -37,7 +38,7 @@ __global__ void lightning_scan_kernel(const float* __restrict__ proj, int ld, in
     const float* row = proj + (size_t)tok * ld;
     for (int i = threadIdx.x; i < 2 * dk + n; i += blockDim.x) {
       const int col = i < dk ? q_off + h * dk + i : (i < 2 * dk ? k_off + h * dk + (i - dk) : v_off + h * dv + e0 + (i - 2 * dk));
-      buf[i] = silu_f(row[col]);
+      buf[i] = act ? silu_f(row[col]) : row[col];
     }
   };
   fetch(first, qk);
@@ -64,6 +65,36 @@ __global__ void lightning_scan_kernel(const float* __restrict__ proj, int ld, in
   for (int i = threadIdx.x; i < dk * n; i += blockDim.x) st[(size_t)(i / n) * dv + e0 + i % n] = S[i];
 }
 
+// Queries and keys made ready for the recurrence, in place in the fp32 projection rows: among the first `rot`
+// numbers of every head, number i turns with number i + rot/2 by the angle float(position) * freq[i] (formed, like
+// its cosine and sine, in fp32); keys are then multiplied by `k_scale`.  A warp per (token, q or k head).
+constexpr int RS_WARPS = 4;
+__global__ void __launch_bounds__(RS_WARPS * 32)
+rotate_scale_kernel(float* __restrict__ proj, int ld, int q_off, int k_off, const float* __restrict__ freq, int rot,
+                    const int* __restrict__ token_pos, int T, int H, int dk, float k_scale) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long item = (long long)blockIdx.x * RS_WARPS + warp;
+  if (item >= (long long)T * 2 * H) return;
+  const int t = (int)(item / (2 * H)), hh = (int)(item - (long long)t * 2 * H);
+  const bool is_k = hh >= H;
+  const int h = is_k ? hh - H : hh;
+  const float p = (float)token_pos[t];
+  const float sc = is_k ? k_scale : 1.0f;
+  pdl_wait();
+  float* u = proj + (size_t)t * ld + (is_k ? k_off : q_off) + (size_t)h * dk;
+  const int rh = rot / 2;
+  for (int i = lane; i < rh; i += 32) {
+    const float a = u[i], b = u[i + rh];
+    float sn, cs;
+    sincosf(p * freq[i], &sn, &cs);
+    u[i] = (a * cs - b * sn) * sc;
+    u[i + rh] = (b * cs + a * sn) * sc;
+  }
+  if (is_k && sc != 1.0f)
+    for (int i = rot + lane; i < dk; i += 32) u[i] *= sc;
+}
+
 // Common qk sizes: a thread keeps its column of the state in registers, and a sequence's tokens of one step
 // are cut into segments that run side by side.
 //   pass 1 (LOCAL): every segment runs from a zero state and leaves its end state L_i; a sequence's first
@@ -76,7 +107,7 @@ __global__ void __launch_bounds__(128)
 lightning_segments_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                           const int* __restrict__ tiles, int n_tiles, const int* __restrict__ seq_slot,
                           const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ local,
-                          float* __restrict__ start_copy, float* __restrict__ out, int ldo, int H, int dv) {
+                          float* __restrict__ start_copy, float* __restrict__ out, int ldo, int H, int dv, int act) {
   pdl_launch_dependents();
   __shared__ __align__(16) float qk[2][2 * DK];
   const int tile = blockIdx.x, h = blockIdx.y;
@@ -134,7 +165,7 @@ lightning_segments_kernel(const float* __restrict__ proj, int ld, int q_off, int
 #pragma unroll
     for (int j = 0; j < PER_T; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
-      if (i < 2 * DK) buf[i] = silu_f(raw[j]);
+      if (i < 2 * DK) buf[i] = act ? silu_f(raw[j]) : raw[j];
     }
   };
   fetch(first);
@@ -144,7 +175,7 @@ lightning_segments_kernel(const float* __restrict__ proj, int ld, int q_off, int
   __syncthreads();
   for (int n = 0; n < count; ++n) {
     const float* cur = qk[n & 1];
-    const float v = live ? silu_f(v_raw) : 0.f;
+    const float v = live ? (act ? silu_f(v_raw) : v_raw) : 0.f;
     const bool more = n + 1 < count;
     if (more) {
       v_raw = vcol[(size_t)(first + n + 1) * ld];
@@ -184,22 +215,22 @@ lightning_segments_kernel(const float* __restrict__ proj, int ld, int q_off, int
 template <int DK>
 static int launch_segments(const float* proj, int ld, int q_off, int k_off, int v_off, const int* tiles, int n_tiles,
                            int direct, const int* seq_slot, const float* decay, float* state, float* scratch,
-                           float* out, int ldo, int H, int dv, cudaStream_t stream) {
+                           float* out, int ldo, int H, int dv, int act, cudaStream_t stream) {
   const dim3 grid(n_tiles, H, (dv + 127) / 128), block(128);
   float* local = scratch;
   float* start_copy = scratch ? scratch + (size_t)n_tiles * H * DK * dv : nullptr;
   if (direct) {
     launch_kernel(lightning_segments_kernel<DK, false, true>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off,
-                  tiles, n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv);
+                  tiles, n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv, act);
     return launch_status();
   }
   if (!scratch) return DLGO_ERR_SIZE;
   launch_kernel(lightning_segments_kernel<DK, true, false>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off, tiles,
-                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv);
+                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv, act);
   int st = launch_status();
   if (st != DLGO_OK) return st;
   launch_kernel(lightning_segments_kernel<DK, false, false>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off, tiles,
-                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv);
+                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv, act);
   return launch_status();
 }
 
@@ -216,10 +247,10 @@ DLGO_EXPORT int dlgo_lightning_segments_takes(int dk) { return dk == 32 || dk ==
 DLGO_EXPORT int dlgo_lightning_segments(const float* proj, int ld, int q_off, int k_off, int v_off, const int* tiles,
                                         int n_tiles, int direct, const int* seq_slot, const float* decay,
                                         float* state, float* scratch, float* out, int ldo, int H, int dk, int dv,
-                                        cudaStream_t stream) {
+                                        int act, cudaStream_t stream) {
   if (n_tiles <= 0) return DLGO_OK;
   if (H <= 0 || dv <= 0 || n_tiles > 65535 * 32) return DLGO_ERR_SIZE;
-#define SEG_ARGS proj, ld, q_off, k_off, v_off, tiles, n_tiles, direct, seq_slot, decay, state, scratch, out, ldo, H, dv, stream
+#define SEG_ARGS proj, ld, q_off, k_off, v_off, tiles, n_tiles, direct, seq_slot, decay, state, scratch, out, ldo, H, dv, act, stream
   if (dk == 32) return launch_segments<32>(SEG_ARGS);
   if (dk == 64) return launch_segments<64>(SEG_ARGS);
   if (dk == 128) return launch_segments<128>(SEG_ARGS);
@@ -230,7 +261,7 @@ DLGO_EXPORT int dlgo_lightning_segments(const float* proj, int ld, int q_off, in
 // state [slots, H, dk, dv] fp32; out [T, ldo] fp32 (heads side by side, dv each)
 DLGO_EXPORT int dlgo_lightning_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const int* tiles,
                                     int n_seqs, const int* seq_slot, const float* decay, float* state, float* out,
-                                    int ldo, int H, int dk, int dv, cudaStream_t stream) {
+                                    int ldo, int H, int dk, int dv, int act, cudaStream_t stream) {
   if (n_seqs <= 0) return DLGO_OK;
   if (H <= 0 || dk <= 0 || dv <= 0) return DLGO_ERR_SIZE;
   // as many of a head's value columns per block as keep the block's part of the state within 96 KB
@@ -244,6 +275,20 @@ DLGO_EXPORT int dlgo_lightning_scan(const float* proj, int ld, int q_off, int k_
   if (threads > 256) threads = 256;
   if (threads < 64) threads = 64;
   launch_kernel(lightning_scan_kernel, dim3(n_seqs, H, (dv + dvc - 1) / dvc), dim3(threads), smem, stream, proj, ld,
-                q_off, k_off, v_off, tiles, seq_slot, decay, state, out, ldo, H, dk, dv, dvc);
+                q_off, k_off, v_off, tiles, seq_slot, decay, state, out, ldo, H, dk, dv, dvc, act);
+  return launch_status();
+}
+
+// proj [T, ld] fp32, rewritten in place: q heads at q_off, k heads at k_off (H heads of dk numbers each);
+// freq [rot / 2] fp32 (may be null with rot == 0); token_pos [T] int32
+DLGO_EXPORT int dlgo_rotate_scale(float* proj, int ld, int q_off, int k_off, const float* freq, int rot,
+                                  const int* token_pos, int T, int H, int dk, float k_scale, cudaStream_t stream) {
+  if (T <= 0) return DLGO_OK;
+  if (H <= 0 || dk <= 0 || rot < 0 || rot > dk || rot % 2 || (rot > 0 && freq == nullptr)) return DLGO_ERR_SIZE;
+  const long long items = (long long)T * 2 * H;
+  const long long blocks = (items + RS_WARPS - 1) / RS_WARPS;
+  if (blocks > 0x7fffffffLL) return DLGO_ERR_SIZE;
+  launch_kernel(rotate_scale_kernel, dim3((unsigned)blocks), dim3(RS_WARPS * 32), 0, stream, proj, ld, q_off, k_off, freq,
+                rot, token_pos, T, H, dk, k_scale);
   return launch_status();
 }

@@ -4,7 +4,8 @@
 //                  router outputs, choice scores c = s + correction, group-limited choice of `top` outputs
 //                  (outputs form `groups` equal groups of neighbours; a group's score is its largest choice
 //                  score; only outputs of the `keep` best groups can be chosen, the others count as minus
-//                  infinity), weights = the chosen outputs' s (optionally renormalised).  A further row of Wr
+//                  infinity), weights = the chosen outputs' s (optionally renormalised).  A bias on the logits
+//                  (`zbias`, one number per output) is part of z: it moves scores and weights alike.  A further row of Wr
 //                  (`has_gate`) gives a per-token gate sigmoid(w_g . h) for a shared expert.
 // 2. moe_plan:     (token, choice) pairs sorted by expert: offsets per expert, the sorted pair list, and a list
 //                  of row tiles (expert, first row), all on the device: nothing returns to the host, so the
@@ -147,12 +148,12 @@ constexpr int RC_WARPS = 4;
 
 // One token's choice by one warp; zt / ct / gt are the warp's scratch rows (rows, n and groups floats).
 __device__ __forceinline__ void choose_token(const float* __restrict__ zg, const float* __restrict__ corr,
-                                             int* __restrict__ idx, float* __restrict__ wt, float* __restrict__ gate,
+                                             const float* __restrict__ zbias, int* __restrict__ idx, float* __restrict__ wt, float* __restrict__ gate,
                                              int t, int n, int has_gate, int top, int groups, int keep,
                                              int sigmoid_scores, int renormalize, float* zt, float* ct, float* gt,
                                              int lane) {
   const int rows = n + (has_gate ? 1 : 0);
-  for (int j = lane; j < rows; j += 32) zt[j] = zg[(size_t)t * rows + j];
+  for (int j = lane; j < rows; j += 32) zt[j] = zg[(size_t)t * rows + j] + (zbias != nullptr && j < n ? zbias[j] : 0.f);
   __syncwarp();
   if (has_gate && lane == 0) gate[t] = 1.f / (1.f + expf(-zt[n]));
   if (sigmoid_scores) {
@@ -217,7 +218,8 @@ __device__ __forceinline__ void choose_token(const float* __restrict__ zg, const
 }
 
 __global__ void __launch_bounds__(RC_WARPS * 32)
-moe_choose_kernel(const float* __restrict__ zg, const float* __restrict__ corr, int* __restrict__ idx,
+moe_choose_kernel(const float* __restrict__ zg, const float* __restrict__ corr, const float* __restrict__ zbias,
+                  int* __restrict__ idx,
                   float* __restrict__ wt, float* __restrict__ gate, int tokens, int n, int has_gate, int top, int groups,
                   int keep, int sigmoid_scores, int renormalize) {
   extern __shared__ float rt_smem[];
@@ -228,7 +230,7 @@ moe_choose_kernel(const float* __restrict__ zg, const float* __restrict__ corr, 
   const int t = blockIdx.x * RC_WARPS + warp;
   pdl_wait();
   if (t >= tokens) return;
-  choose_token(zg, corr, idx, wt, gate, t, n, has_gate, top, groups, keep, sigmoid_scores, renormalize, zt, zt + rows,
+  choose_token(zg, corr, zbias, idx, wt, gate, t, n, has_gate, top, groups, keep, sigmoid_scores, renormalize, zt, zt + rows,
                zt + rows + n, lane);
 }
 
@@ -286,7 +288,8 @@ moe_plan_kernel(const int* __restrict__ idx, int pairs, int n_experts, int tile_
 
 // Choice and plan of a step of few tokens in one launch: one block, a warp per token in turn, then the plan.
 __global__ void __launch_bounds__(PLAN_THREADS)
-moe_choose_plan_kernel(const float* __restrict__ zg, const float* __restrict__ corr, int* __restrict__ idx,
+moe_choose_plan_kernel(const float* __restrict__ zg, const float* __restrict__ corr,
+                       const float* __restrict__ zbias, int* __restrict__ idx,
                        float* __restrict__ wt, float* __restrict__ gate, int tokens, int n, int has_gate, int top,
                        int groups, int keep, int sigmoid_scores, int renormalize, int n_experts, int tile_rows,
                        int* __restrict__ offsets, int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
@@ -301,7 +304,7 @@ moe_choose_plan_kernel(const float* __restrict__ zg, const float* __restrict__ c
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
   pdl_wait();
   for (int t = warp; t < tokens; t += n_warps) {
-    choose_token(zg, corr, idx, wt, gate, t, n, has_gate, top, groups, keep, sigmoid_scores, renormalize, zt, zt + rows,
+    choose_token(zg, corr, zbias, idx, wt, gate, t, n, has_gate, top, groups, keep, sigmoid_scores, renormalize, zt, zt + rows,
                  zt + rows + n, lane);
     __syncwarp();
   }
@@ -576,7 +579,8 @@ static void launch_logits(const void* h, int ldh, const float* Wr, float* z, int
 
 // Two launches: the logits z [tokens, n (+ 1)] (scratch, fp32), then the choice.  With plan_experts > 0 and few
 // tokens the second launch also makes the plan (as dlgo_moe_plan would from idx); *fused says whether it did.
-DLGO_EXPORT int dlgo_moe_router(const void* h, int dtype, int ldh, const float* Wr, const float* corr, float* z, int* idx,
+DLGO_EXPORT int dlgo_moe_router(const void* h, int dtype, int ldh, const float* Wr, const float* corr,
+                                const float* zbias, float* z, int* idx,
                                 float* wt, float* gate, int tokens, int d, int n, int has_gate, int top, int groups,
                                 int keep, int sigmoid_scores, int renormalize, int plan_experts, int tile_rows,
                                 int* offsets, int* sorted_pair, int* tile_expert, int* tile_row0, int* n_tiles,
@@ -598,7 +602,7 @@ DLGO_EXPORT int dlgo_moe_router(const void* h, int dtype, int ldh, const float* 
     const size_t both = sizeof(float) * warps * ((size_t)rows + n + groups) + sizeof(int) * 2 * (size_t)plan_experts;
     const int pairs = tokens * top;
     if (both <= 48 * 1024 && tile_rows > 0 && max_tiles >= (pairs + tile_rows - 1) / tile_rows + plan_experts) {
-      launch_kernel(moe_choose_plan_kernel, dim3(1), dim3(warps * 32), both, stream, (const float*)z, corr, idx, wt, gate,
+      launch_kernel(moe_choose_plan_kernel, dim3(1), dim3(warps * 32), both, stream, (const float*)z, corr, zbias, idx, wt, gate,
                     tokens, n, has_gate, top, groups, keep, sigmoid_scores, renormalize, plan_experts, tile_rows, offsets,
                     sorted_pair, tile_expert, tile_row0, n_tiles, max_tiles);
       *fused = 1;
@@ -606,7 +610,7 @@ DLGO_EXPORT int dlgo_moe_router(const void* h, int dtype, int ldh, const float* 
     }
   }
   launch_kernel(moe_choose_kernel, dim3((tokens + RC_WARPS - 1) / RC_WARPS), dim3(RC_WARPS * 32), smem, stream,
-                (const float*)z, corr, idx, wt, gate, tokens, n, has_gate, top, groups, keep, sigmoid_scores, renormalize);
+                (const float*)z, corr, zbias, idx, wt, gate, tokens, n, has_gate, top, groups, keep, sigmoid_scores, renormalize);
   return launch_status();
 }
 

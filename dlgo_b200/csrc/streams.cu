@@ -5,8 +5,9 @@
 //            result y goes back into every stream at once, from the old values:
 //            X'[t, q, :] = sum_r M[r, q] X[t, r, :] + b[q] * y[t, :]            (M indexed [from, to])
 //   norms    Dynamic Tanh: tanh(alpha * u) * w + beta (no statistics); RMS: u / sqrt(mean(u^2) + eps) * w
-//   bias_act act(z + bias): none, relu(z)^2, silu, tanh-form gelu
-//   gated    rms(o) * w * sigmoid(g)
+//   bias_act act(z + bias): none, relu(z)^2, silu, tanh-form gelu, tanh
+//   gated    rms(o) * w * gate(g) * c, the mean over the whole row or over each group of neighbours (a head);
+//            gate is sigmoid or silu, w may be absent
 //
 // One launch does a whole hand-over between two sublayers: the write of sublayer k's result, the read for
 // sublayer k+1 and its norm.  Everything is computed in fp32; TO is the type handed to the next contraction.
@@ -16,7 +17,8 @@ namespace dlgo {
 
 constexpr int MAX_STREAMS = 8;
 enum { NORM_NONE = 0, NORM_RMS = 1, NORM_DYT = 2 };
-enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_SILU = 2, ACT_GELU_TANH = 3 };
+enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_SILU = 2, ACT_GELU_TANH = 3, ACT_TANH = 4 };
+enum { GATE_SIGMOID = 0, GATE_SILU = 1 };
 
 struct StreamsStep {
   float* X;             // [T, s, d]
@@ -165,6 +167,7 @@ __device__ __forceinline__ float activate(float z, int act) {
     case ACT_RELU2: { const float r = fmaxf(z, 0.f); return r * r; }
     case ACT_SILU: return z / (1.0f + expf(-z));
     case ACT_GELU_TANH: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    case ACT_TANH: return tanhf(z);
     default: return z;
   }
 }
@@ -198,10 +201,16 @@ __global__ void bias_act_kernel(const float* z, int ldz, const float* __restrict
   }
 }
 
-// out[t, :] = o[t, :] / sqrt(mean(o[t, :]^2) + eps) * w * sigmoid(g[t, :]);  o, g fp32 with row strides
+__device__ __forceinline__ float gate_of(float g, int gate_act) {
+  const float sg = 1.0f / (1.0f + expf(-g));
+  return gate_act == GATE_SILU ? g * sg : sg;
+}
+
+// out[t, :] = o[t, :] / sqrt(mean(o[t, :]^2) + eps) * w * gate(g[t, :]) * c;  o, g fp32 with row strides; w may be null
 template <typename TO>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, int ldg,
-                                     const float* __restrict__ w, TO* __restrict__ out, int n, float eps) {
+                                     const float* __restrict__ w, TO* __restrict__ out, int n, float eps, int gate_act,
+                                     float c) {
   pdl_launch_dependents();
   __shared__ float scratch[32];
   __shared__ float scale_s;
@@ -214,9 +223,34 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, int ldo, const
   ss = block_sum(ss, scratch);
   if (threadIdx.x == 0) scale_s = 1.0f / sqrtf(ss / (float)n + eps);
   __syncthreads();
-  const float sc = scale_s;
+  const float sc = scale_s * c;
   for (int i = threadIdx.x; i < n; i += blockDim.x)
-    out[(size_t)t * n + i] = from_float<TO>(orow[i] * sc * w[i] * (1.0f / (1.0f + expf(-grow[i]))));
+    out[(size_t)t * n + i] = from_float<TO>(orow[i] * sc * (w != nullptr ? w[i] : 1.0f) * gate_of(grow[i], gate_act));
+}
+
+// The same with the mean taken over each group of `group` neighbours (a head) on its own: a warp per (token, group).
+constexpr int GG_WARPS = 4;
+template <typename TO>
+__global__ void __launch_bounds__(GG_WARPS * 32)
+gated_groupnorm_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, int ldg,
+                       const float* __restrict__ w, TO* __restrict__ out, int T, int n, int group, float eps,
+                       int gate_act, float c) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int groups = n / group;
+  const long long item = (long long)blockIdx.x * GG_WARPS + warp;
+  pdl_wait();
+  if (item >= (long long)T * groups) return;
+  const int t = (int)(item / groups), gi = (int)(item - (long long)t * groups);
+  const float* orow = o + (size_t)t * ldo + (size_t)gi * group;
+  const float* grow = g + (size_t)t * ldg + (size_t)gi * group;
+  float ss = 0.f;
+  for (int i = lane; i < group; i += 32) ss = fmaf(orow[i], orow[i], ss);
+  ss = warp_sum(ss);
+  const float sc = c / sqrtf(ss / (float)group + eps);
+  for (int i = lane; i < group; i += 32)
+    out[(size_t)t * n + (size_t)gi * group + i] =
+        from_float<TO>(orow[i] * sc * (w != nullptr ? w[(size_t)gi * group + i] : 1.0f) * gate_of(grow[i], gate_act));
 }
 
 }  // namespace dlgo
@@ -245,7 +279,7 @@ DLGO_EXPORT int dlgo_streams_step(float* X, int T, int s, int d, float* y, const
 DLGO_EXPORT int dlgo_bias_act(const float* z, int ldz, const float* bias, void* out, int out_dtype, int ldo, int T,
                               int n, int act, cudaStream_t stream) {
   if (T <= 0 || n <= 0) return DLGO_OK;
-  if (act < ACT_NONE || act > ACT_GELU_TANH) return DLGO_ERR_SIZE;
+  if (act < ACT_NONE || act > ACT_TANH) return DLGO_ERR_SIZE;
   const size_t total = ((size_t)T * n + 3) / 4;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
@@ -259,17 +293,31 @@ DLGO_EXPORT int dlgo_bias_act(const float* z, int ldz, const float* bias, void* 
   return launch_status();
 }
 
+// group: numbers per group whose mean square is taken together (n: the whole row); gate_act: GATE_*; c: a constant factor
 DLGO_EXPORT int dlgo_gated_rmsnorm(const float* o, int ldo, const float* g, int ldg, const float* w, void* out,
-                                   int out_dtype, int T, int n, float eps, cudaStream_t stream) {
+                                   int out_dtype, int T, int n, float eps, int group, int gate_act, float c,
+                                   cudaStream_t stream) {
   if (T <= 0) return DLGO_OK;
-  if (n <= 0) return DLGO_ERR_SIZE;
+  if (n <= 0 || group <= 0 || n % group || (gate_act != GATE_SIGMOID && gate_act != GATE_SILU)) return DLGO_ERR_SIZE;
+  if (out_dtype != DLGO_F32 && out_dtype != DLGO_BF16) return DLGO_ERR_DTYPE;
+  if (group < n) {
+    const long long items = (long long)T * (n / group);
+    const long long blocks = (items + GG_WARPS - 1) / GG_WARPS;
+    if (blocks > 0x7fffffffLL) return DLGO_ERR_SIZE;
+    if (out_dtype == DLGO_F32)
+      launch_kernel(gated_groupnorm_kernel<float>, dim3((unsigned)blocks), dim3(GG_WARPS * 32), 0, stream, o, ldo, g, ldg,
+                    w, (float*)out, T, n, group, eps, gate_act, c);
+    else
+      launch_kernel(gated_groupnorm_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(GG_WARPS * 32), 0, stream, o, ldo,
+                    g, ldg, w, (__nv_bfloat16*)out, T, n, group, eps, gate_act, c);
+    return launch_status();
+  }
   const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
   if (out_dtype == DLGO_F32)
-    launch_kernel(gated_rmsnorm_kernel<float>, dim3(T), dim3(threads), 0, stream, o, ldo, g, ldg, w, (float*)out, n, eps);
-  else if (out_dtype == DLGO_BF16)
-    launch_kernel(gated_rmsnorm_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, o, ldo, g, ldg, w,
-                  (__nv_bfloat16*)out, n, eps);
+    launch_kernel(gated_rmsnorm_kernel<float>, dim3(T), dim3(threads), 0, stream, o, ldo, g, ldg, w, (float*)out, n, eps,
+                  gate_act, c);
   else
-    return DLGO_ERR_DTYPE;
+    launch_kernel(gated_rmsnorm_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, o, ldo, g, ldg, w,
+                  (__nv_bfloat16*)out, n, eps, gate_act, c);
   return launch_status();
 }

@@ -3,7 +3,8 @@ from .base import Block, CacheNeed, FeedForward, Mixer, Norm, ParamSpec, Part, P
 from .registry import (BLOCKS, CONNECTIONS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
                        register_block, register_connection, register_feed_forward, register_mixer, register_norm,
                        register_position_encoding)
-from . import attention, block, embedding, experts, feedforward, latent_attention, lightning, norm, rope  # noqa: F401  (fill the registries)
+from . import (attention, block, embedding, experts, feedforward, latent_attention, lightning, norm, parallel, rope,  # noqa: F401
+               timemix)  # noqa: F401  (fill the registries)
 
 __all__ = [
     "BLOCKS", "Block", "CONNECTIONS", "CacheNeed", "EMBEDDINGS", "FEED_FORWARDS", "FeedForward", "HEADS", "MIXERS", "Mixer",

@@ -21,7 +21,7 @@ import torch
 
 from ..csrc import kernels as K
 from .base import CacheNeed, Mixer, ParamSpec, PositionEncoding
-from .linear import ADD_F32, STORE, STORE_F32, Linear
+from .linear import ADD_F32, STORE, STORE_F32, Linear, stack_rows
 from .registry import MIXERS
 
 _CLUSTER_MAX = int(os.environ.get("DLGO_ATTN_CLUSTER_MAX", 8))     # slices up to this many combine in a cluster
@@ -339,5 +339,103 @@ class KeysAsValuesAttention(GQAAttention):
         self._project_out(out, residual, ctx)
 
 
+class WholeNormAttention(GQAAttention):
+    """Grouped-query softmax attention without positions, whose queries and keys are normed over their WHOLE
+    projection, whose keys and values may differ in size, and whose heads are gated:
+
+        q = Wq h,  k = Wk h,  v = Wv h                        (H x qk_dim, G x qk_dim, G x v_dim numbers)
+        q <- q / sqrt(mean over all H qk_dim numbers of q^2 + eps) * wq      (``qk_norm``; likewise k with wk)
+        out_h = softmax over the visible keys of (q_h . k_g * scale) v_g     (g = h // (H / G); ``window`` w: keys j
+                                                                             with 0 <= i - j < w)
+        out_h <- out_h * sigmoid(Wg h)_h                                     (``head_gate``: one number per head)
+        result = Wo [out_1 .. out_H] * out_scale
+
+    Heads are laid out ``head_dim`` = max(qk_dim, v_dim) (rounded up to a multiple of 8) numbers wide with zeros
+    behind their own numbers, so that keys and values share the page shape and the kernels of
+    :class:`GQAAttention` run unchanged; the output projection gets zero columns.  The projection's result stays
+    fp32 until norm and gate are done (one kernel, which also appends to the cache).  ``names``: tensor names
+    below the part's prefix."""
+
+    head_multiple = 8
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, qk_dim: int, v_dim: int, scale: float,
+                 eps: float = 1e-6, window: Optional[int] = None, qk_norm: bool = True, head_gate: bool = False,
+                 cache_group: str = "full", out_scale: float = 1.0, names: Optional[Mapping[str, str]] = None):
+        self.qk_dim, self.v_dim = int(qk_dim), int(v_dim)
+        if self.qk_dim <= 0 or self.v_dim <= 0:
+            raise ValueError("qk_dim and v_dim must be positive")
+        padded = -(-max(self.qk_dim, self.v_dim) // self.head_multiple) * self.head_multiple
+        super().__init__(hidden_size, num_heads, num_kv_heads, padded, scale, window, None, cache_group)
+        self.params = dict(hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads, qk_dim=qk_dim,
+                           v_dim=v_dim, scale=scale, eps=eps, window=window, qk_norm=qk_norm, head_gate=head_gate,
+                           cache_group=cache_group, out_scale=out_scale, names=names)
+        self.eps = float(eps)
+        self.qk_norm, self.head_gate = bool(qk_norm), bool(head_gate)
+        self.out_scale = float(out_scale)
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "q_norm": "q_norm.weight",
+                      "k_norm": "k_norm.weight", "gate": "g_proj.weight", "out": "o_proj.weight"}
+        self.names.update(names or {})
+        self.w_in: Optional[Linear] = None        # rows q | k | v | gate
+        self.w_qnorm: Optional[torch.Tensor] = None
+        self.w_knorm: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n, d = self.names, self.hidden_size
+        H, G, dk, dv = self.num_heads, self.num_kv_heads, self.qk_dim, self.v_dim
+        specs = {n["q"]: ParamSpec((H * dk, d)), n["k"]: ParamSpec((G * dk, d)), n["v"]: ParamSpec((G * dv, d)),
+                 n["out"]: ParamSpec((d, H * dv))}
+        if self.qk_norm:
+            specs[n["q_norm"]] = ParamSpec((H * dk,), "one_plus_normal")
+            specs[n["k_norm"]] = ParamSpec((G * dk,), "one_plus_normal")
+        if self.head_gate:
+            specs[n["gate"]] = ParamSpec((H, d))
+        return specs
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        n = self.names
+        rows = [runtime.compute_copy(get(n[k])) for k in ("q", "k", "v")]
+        if self.head_gate:
+            rows.append(runtime.compute_copy(get(n["gate"])))
+        self.w_in = Linear(stack_rows(rows), runtime)
+        wo = runtime.compute_copy(get(n["out"]))
+        hd, dv, H = self.head_dim, self.v_dim, self.num_heads
+        if dv != hd:        # zero columns where the heads' layout has zeros
+            wide = torch.zeros((wo.shape[0], H, hd), dtype=wo.dtype, device=wo.device)
+            wide[:, :, :dv] = wo.view(wo.shape[0], H, dv)
+            wo = wide.view(wo.shape[0], H * hd)
+        self.wo = Linear(wo.contiguous(), runtime)
+        if self.qk_norm:    # norms are 32-bit in every precision
+            self.w_qnorm = get(n["q_norm"]).to(torch.float32).contiguous()
+            self.w_knorm = get(n["k_norm"]).to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
+                state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
+        T = ctx.n_tokens
+        act = self.w_in.weight.dtype
+        n_cols = self.w_in.out_features
+        decode_kernel, mma, n_splits, scratch, counters, pages = self._decode_plan(ctx, cache, act)
+        if _QKV_SUM and self.w_in.sums_slices_at_memory(T):
+            # few tokens: the projection's K-slices add themselves into one fp32 sum that is zero between steps;
+            # the norm-and-append kernel reads it once and leaves zeros behind
+            proj = ctx.zeros(f"qkvg_sum{n_cols}", T * n_cols, torch.float32)[:T * n_cols].view(T, n_cols)
+            self.w_in(x, ADD_F32, proj)
+            clear = True
+        else:
+            proj = self.w_in(x, STORE_F32)
+            clear = False
+        q, gate = K.wholenorm_append(proj, self.w_qnorm, self.w_knorm, self.eps, ctx.token_pos, ctx.token_seq,
+                                     ctx.seq_slot, cache.page_table, cache.keys, cache.values, self.num_heads,
+                                     self.num_kv_heads, self.qk_dim, self.v_dim, self.head_gate, self.out_scale,
+                                     cache.writes, clear, act)
+        out = torch.empty((T, self.q_dim), dtype=act, device=x.device)
+        self._attend(q, ctx, cache, out, decode_kernel, mma, n_splits, scratch, counters, pages)
+        if gate is None and self.out_scale != 1.0:      # no gates to carry the constant factor
+            gate = torch.full((T, self.num_heads), self.out_scale, dtype=torch.float32, device=x.device)
+        if gate is not None:
+            K.scale_heads(out, gate, self.head_dim)
+        self._project_out(out, residual, ctx)
+
+
 MIXERS.register("gqa_attention", GQAAttention)
+MIXERS.register("wholenorm_attention", WholeNormAttention)
 MIXERS.register("keys_as_values_attention", KeysAsValuesAttention)

@@ -197,7 +197,57 @@ class PostNormBlock(Block):
         ctx.residual_copy = (residual, x)
 
 
+class ResultNormBlock(Block):
+    """Norm on the sublayer's RESULT only: ``x <- x + norm1(mixer(x))``, then ``x <- x + norm2(ffn(x))``; the
+    sublayers read x itself.  A layer without a feed-forward ends after the first line.  The norms are any that
+    :func:`kernels.add_normed` knows (a layer norm with a weight, an RMS norm: ``normed_kind``, ``weight``, ``eps``).
+    The residual stream stays fp32; a sublayer adds its result into a zeroed fp32 [tokens, hidden] buffer as it
+    would into a residual stream, and ONE launch norms that buffer, adds it to x, leaves the buffer zero and makes
+    the copy of x in the run's type that the next contractions read.  A sublayer that wants x unrounded (a
+    recurrence's inputs) finds the fp32 stream as ``ctx.sublayer_input_f32``."""
+
+    handles_pending = False
+
+    def __init__(self, mixer: Any, ffn: Any, norms: Mapping[str, Any], connections: Any = None):
+        super().__init__(mixer, ffn, norms, connections)
+        if mixer is None:
+            raise ValueError("a block needs a mixer")
+        self.sublayers = []
+        for part, role in ((mixer, "mixer_norm"), (ffn, "ffn_norm")):
+            if part is None:
+                continue
+            n = self.norms.get(role)
+            if n is None or not (hasattr(n, "normed_kind") and hasattr(n, "weight") and hasattr(n, "eps")):
+                raise ValueError(f"a result-norm block needs a layer norm or an RMS norm as {role!r}")
+            self.sublayers.append((part, n))
+
+    def forward(self, residual: torch.Tensor, ctx: Any, cache: Any, state: Optional[torch.Tensor],
+                positions: Mapping[str, PositionEncoding]) -> None:
+        T, d = residual.shape
+        dtype = ctx.runtime.dtype
+        y = ctx.zeros(f"sublayer_out{d}", T * d, torch.float32)[:T * d].view(T, d)
+        if dtype == torch.float32:
+            x = residual
+        else:
+            kept = getattr(ctx, "residual_copy", None)
+            x = kept[1] if kept is not None and kept[0] is residual else \
+                K.scaled_add_rmsnorm(residual, None, None, None, 1.0, 0.0, dtype)
+        ctx.sublayer_input_f32 = residual
+        for part, norm in self.sublayers:
+            if part is self.mixer:
+                part.forward(x, y, ctx, cache, state, positions)
+            else:
+                part.forward(x, y, ctx)
+            ctx.settle(y)
+            copy = K.add_normed(residual, y, norm.weight, norm.eps, None if dtype == torch.float32 else dtype,
+                                norm.normed_kind, clear_y=True)
+            x = residual if copy is None else copy
+        ctx.sublayer_input_f32 = None
+        ctx.residual_copy = (residual, x)
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("result_norm", ResultNormBlock)
 BLOCKS.register("hyper_prenorm", HyperPreNormBlock)
 BLOCKS.register("postnorm", PostNormBlock)
 CONNECTIONS.register("hyper_connection", HyperConnection)

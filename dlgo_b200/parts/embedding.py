@@ -7,7 +7,7 @@ models/llm/loader.go:74-76).
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, Optional
+from typing import Any, Callable, Dict, Optional, Sequence
 
 import torch
 
@@ -18,24 +18,43 @@ from .registry import EMBEDDINGS, HEADS
 
 
 class TokenEmbedding(Part):
-    """``name``: the table's tensor name below the part's prefix."""
+    """``name``: the table's tensor name below the part's prefix.  ``norm``: a norm applied to the looked-up rows
+    before they become the residual stream, as ``(kind, params)`` of the norm registry (its tensor names are
+    relative to the embedding's prefix as well); it must offer ``forward_in_place`` on fp32 rows."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, name: str = "weight"):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, name=name)
+    def __init__(self, vocab_size: int, hidden_size: int, name: str = "weight", norm: Optional[Sequence[Any]] = None):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, name=name, norm=norm)
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
         self.name = name
         self.table: Optional[torch.Tensor] = None
+        self.norm: Any = None
+        if norm is not None:
+            from ..config.spec import PartSpec
+            from .registry import NORMS
+            kind, params = norm
+            self.norm = NORMS.build(PartSpec(kind, dict(params)))
+            if not hasattr(self.norm, "forward_in_place"):
+                raise ValueError(f"the norm {kind!r} cannot rewrite fp32 rows in place")
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {self.name: ParamSpec((self.vocab_size, self.hidden_size))}
+        specs = {self.name: ParamSpec((self.vocab_size, self.hidden_size))}
+        if self.norm is not None:
+            specs.update(self.norm.param_specs())
+        return specs
 
     def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
         self.table = runtime.compute_copy(get(self.name)).contiguous()
+        if self.norm is not None:
+            self.norm.load(get, runtime)
 
     def forward(self, token_ids: torch.Tensor, copies: Optional[int] = None) -> torch.Tensor:
         """fp32 rows [T, hidden]; with ``copies`` = s, [T, s, hidden] with every copy equal (residual streams)."""
-        return K.embed(token_ids, self.table, copies=copies)
+        if self.norm is None:
+            return K.embed(token_ids, self.table, copies=copies)
+        if copies is not None:
+            raise ValueError("a normed embedding feeds a single residual stream")
+        return self.norm.forward_in_place(K.embed(token_ids, self.table))
 
 
 class LinearHead(Part):

@@ -1,12 +1,14 @@
 """Routed experts: a mixture-of-experts feed-forward.
 
-    z = Wr h                         router logits, fp32 (the router's weight is kept in fp32)
+    z = Wr h (+ b)                   router logits, fp32 (the router's weight is kept in fp32; ``logit_bias``: a stored
+                                     bias that is part of the logits, unlike ``correction``)
     s = softmax(z)  (or sigmoid(z))  over ALL router outputs
     c = s + correction               choice scores (``correction``: a stored per-output bias used for choosing only)
     outputs form ``group_count`` equal groups of neighbours; a group's score is its largest c; only outputs of
     the ``group_keep`` best groups can be chosen (the others count as minus infinity); the ``top`` largest c win
     y = sum over the chosen e of s_e * expert_e(h)            (``renormalize``: s_e / sum of the chosen s)
     expert_e(h) = Wdown_e act(Wup_e h)                        for e < num_experts
+                  (``gated``: Wdown_e (silu(Wgate_e h) * (Wup_e h)), a third matrix per expert)
     expert_e(h) = h                                           for the ``identity_experts`` outputs after them
     y += gate * shared(h),  gate = sigmoid(w_g . h) per token (``shared_size``, ``shared_gate``)
 
@@ -47,11 +49,16 @@ class RoutedExperts(FeedForward):
                  identity_experts: int = 0, group_count: int = 1, group_keep: int = 1, score: str = "softmax",
                  renormalize: bool = False, correction: bool = False, activation: str = "relu2",
                  shared_size: Optional[int] = None, shared_gate: bool = False,
-                 names: Optional[Mapping[str, str]] = None):
+                 names: Optional[Mapping[str, str]] = None, logit_bias: bool = False, gated: bool = False):
         super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size, num_experts=num_experts, top=top,
                          identity_experts=identity_experts, group_count=group_count, group_keep=group_keep,
                          score=score, renormalize=renormalize, correction=correction, activation=activation,
-                         shared_size=shared_size, shared_gate=shared_gate, names=names)
+                         shared_size=shared_size, shared_gate=shared_gate, names=names, logit_bias=logit_bias,
+                         gated=gated)
+        self.logit_bias = bool(logit_bias)
+        self.gated = bool(gated)
+        if self.gated and activation != "silu":
+            raise ValueError("gated experts multiply silu(gate) by up: the activation must be 'silu'")
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
         self.num_experts = int(num_experts)
@@ -73,12 +80,14 @@ class RoutedExperts(FeedForward):
         self.act = _ACTS[activation]
         self.shared_size = None if shared_size is None else int(shared_size)
         self.shared_gate = bool(shared_gate) and self.shared_size is not None
-        self.names = {"router": "router.weight", "correction": "router.bias", "expert": "experts.{}.",
+        self.names = {"router": "router.weight", "correction": "router.bias", "logit_bias": "router.logit_bias",
+                      "gate": "gate_proj.weight", "expert": "experts.{}.",
                       "up": "up_proj.weight", "down": "down_proj.weight", "shared_up": "shared.up_proj.weight",
                       "shared_down": "shared.down_proj.weight", "shared_gate": "shared.gate.weight"}
         self.names.update(names or {})
         self.w_router: Optional[torch.Tensor] = None        # fp32 [outputs (+ gate row), hidden]
         self.b_choice: Optional[torch.Tensor] = None
+        self.b_logit: Optional[torch.Tensor] = None
         self.w_up: Optional[torch.Tensor] = None            # [experts, ff, hidden]
         self.w_down: Optional[torch.Tensor] = None          # [experts, hidden, ff]
         self.shared_up: Optional[Linear] = None
@@ -90,8 +99,12 @@ class RoutedExperts(FeedForward):
         specs = {n["router"]: ParamSpec((self.n_outputs, d))}
         if self.correction:
             specs[n["correction"]] = ParamSpec((self.n_outputs,))
+        if self.logit_bias:
+            specs[n["logit_bias"]] = ParamSpec((self.n_outputs,))
         for e in range(self.num_experts):
             p = n["expert"].format(e)
+            if self.gated:
+                specs[p + n["gate"]] = ParamSpec((f, d))
             specs[p + n["up"]] = ParamSpec((f, d))
             specs[p + n["down"]] = ParamSpec((d, f))
         if self.shared_size is not None:
@@ -109,13 +122,18 @@ class RoutedExperts(FeedForward):
         self.w_router = torch.cat(rows, dim=0).contiguous()      # routers are 32-bit in every precision
         if self.correction:
             self.b_choice = get(n["correction"]).to(torch.float32).contiguous()
+        if self.logit_bias:
+            self.b_logit = get(n["logit_bias"]).to(torch.float32).contiguous()
         if self.num_experts:
             ups = [runtime.compute_copy(get(n["expert"].format(e) + n["up"])) for e in range(self.num_experts)]
+            if self.gated:      # an expert's first matrix: its gate rows, then its up rows
+                ups = [torch.cat([runtime.compute_copy(get(n["expert"].format(e) + n["gate"])), up], dim=0)
+                       for e, up in enumerate(ups)]
             downs = [runtime.compute_copy(get(n["expert"].format(e) + n["down"])) for e in range(self.num_experts)]
             self.w_up = torch.stack(ups, dim=0).contiguous()
             self.w_down = torch.stack(downs, dim=0).contiguous()
             self.on_tensor_cores = (_TENSOR_CORES and
-                                    K.moe_gemm_tc_takes(self.w_up.dtype, self.intermediate_size, self.hidden_size) and
+                                    K.moe_gemm_tc_takes(self.w_up.dtype, self.w_up.shape[1], self.hidden_size) and
                                     K.moe_gemm_tc_takes(self.w_down.dtype, self.hidden_size, self.intermediate_size))
         if self.shared_size is not None:
             self.shared_up = Linear(get(n["shared_up"]), runtime)
@@ -132,18 +150,24 @@ class RoutedExperts(FeedForward):
                      (K.MOE_FEW_ROWS if few else K.MOE_TILE_ROWS))
         idx, wt, gate, plan = K.moe_router(x, self.w_router, self.b_choice, self.n_outputs, self.shared_gate, self.top,
                                            self.group_count, self.group_keep, self.sigmoid_scores, self.renormalize,
-                                           plan=(self.num_experts, tile_rows))
+                                           plan=(self.num_experts, tile_rows), logit_bias=self.b_logit)
         pair_out = None
         if self.num_experts:
-            hidden = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
+            # (gated: the first contraction leaves gate | up side by side, and silu(gate) * up is a pass of its own)
+            act = K.ACT_NONE if self.gated else self.act
+            hidden = torch.empty((pairs, self.w_up.shape[1]), dtype=x.dtype, device=x.device)
             pair_out = torch.empty((pairs, d), dtype=x.dtype, device=x.device)    # (sums of these stay fp32)
             if on_tc:
                 # bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
                 rows = K.moe_gather_rows(plan, x, self.top)
-                K.moe_gemm_tc(plan, rows, self.w_up, hidden, False, self.act)
+                K.moe_gemm_tc(plan, rows, self.w_up, hidden, False, act)
+                if self.gated:
+                    hidden = K.swiglu(hidden)
                 K.moe_gemm_tc(plan, hidden, self.w_down, pair_out, True, K.ACT_NONE)
             else:
-                K.moe_gemm(plan, x, self.w_up, hidden, self.top, False, self.act)          # rows gathered by token
+                K.moe_gemm(plan, x, self.w_up, hidden, self.top, False, act)               # rows gathered by token
+                if self.gated:
+                    hidden = K.swiglu(hidden)
                 K.moe_gemm(plan, hidden, self.w_down, pair_out, None, True, K.ACT_NONE)    # rows scattered by pair
         shared = None
         if self.shared_size is not None:

@@ -19,23 +19,28 @@ from .registry import FEED_FORWARDS
 
 
 class SwiGLU(FeedForward):
-    def __init__(self, hidden_size: int, intermediate_size: int):
-        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size)
+    """``names``: tensor names of gate, up and down below the part's prefix."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, names: Optional[Mapping[str, str]] = None):
+        super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size, names=names)
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(names or {})
         self.w_gate_up: Optional[Linear] = None
         self.w_down: Optional[Linear] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
+        n = self.names
         return {
-            "gate_proj.weight": ParamSpec((self.intermediate_size, self.hidden_size)),
-            "up_proj.weight": ParamSpec((self.intermediate_size, self.hidden_size)),
-            "down_proj.weight": ParamSpec((self.hidden_size, self.intermediate_size)),
+            n["gate"]: ParamSpec((self.intermediate_size, self.hidden_size)),
+            n["up"]: ParamSpec((self.intermediate_size, self.hidden_size)),
+            n["down"]: ParamSpec((self.hidden_size, self.intermediate_size)),
         }
 
     def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
-        gate = runtime.compute_copy(get("gate_proj.weight"))
-        up = runtime.compute_copy(get("up_proj.weight"))
+        gate = runtime.compute_copy(get(self.names["gate"]))
+        up = runtime.compute_copy(get(self.names["up"]))
         f, d = self.intermediate_size, self.hidden_size
         self.fused = False
         if runtime.dtype == torch.bfloat16 and f % 16 == 0 and d % 8 == 0:
@@ -46,7 +51,7 @@ class SwiGLU(FeedForward):
             self.fused = True
         else:
             self.w_gate_up = Linear(torch.cat([gate, up], dim=0), runtime)
-        self.w_down = Linear(get("down_proj.weight"), runtime)
+        self.w_down = Linear(get(self.names["down"]), runtime)
 
     def forward(self, x: Any, residual: torch.Tensor, ctx: Any) -> None:
         if self.fused:

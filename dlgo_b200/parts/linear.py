@@ -17,6 +17,16 @@ from ..csrc import kernels as K
 STORE, STORE_F32, ADD_F32 = K.EPI_STORE, K.EPI_STORE_F32, K.EPI_ADD_F32
 
 
+def stack_rows(weights, multiple: int = 8) -> torch.Tensor:
+    """Weights [out_i, in] one below the other, with zero rows at the end up to a multiple of ``multiple`` outputs
+    (rows of a result are then a multiple of 16 bytes in either precision, which the tensor-core stores want)."""
+    w = torch.cat(list(weights), dim=0)
+    pad = -w.shape[0] % multiple
+    if pad:
+        w = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)], dim=0)
+    return w.contiguous()
+
+
 class Linear:
     """``fused_swiglu``: the weight holds gate and up rows in blocks of 16 + 16 and the contraction's
     epilogue writes ``silu(gate) * up`` ([T, out/2]); only the tensor-core kernel offers it

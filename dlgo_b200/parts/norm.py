@@ -1,5 +1,6 @@
 """RMSNorm: ``out = x * (1 / sqrt(mean(x^2) + eps)) * w`` (ops/norm.go:10-32),
-statistics in fp32 on the fp32 residual stream, output in the run's precision."""
+statistics in fp32 on the fp32 residual stream, output in the run's precision.  Beside it: Dynamic Tanh, and the
+layer norm with a weight and no bias."""
 from __future__ import annotations
 
 from typing import Any, Callable, Dict, Optional
@@ -39,6 +40,38 @@ class RMSNorm(Norm):
                       rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``residual += parts.sum(0)`` and the norm of the new rows, in one pass."""
         return K.add_rmsnorm(residual, parts, self.weight, self.eps, self.out_dtype, rows)
+
+
+RMSNorm.normed_kind = K.NORMED_RMS       # for arrangements that norm a sublayer's result (kernels.add_normed)
+
+
+class LayerNorm(Norm):
+    """``out = (x - mean(x)) / sqrt(var(x) + eps) * w`` with the variance as the mean of the squared deviations;
+    a weight, no bias.  ``name``: the tensor's name below the part's prefix."""
+
+    normed_kind = K.NORMED_LAYER
+
+    def __init__(self, size: int, eps: float, name: str = "weight"):
+        super().__init__(size=size, eps=eps, name=name)
+        self.size = int(size)
+        self.eps = float(eps)
+        self.name = name
+        self.weight: Optional[torch.Tensor] = None
+        self.out_dtype: Optional[torch.dtype] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.name: ParamSpec((self.size,), "one_plus_normal")}
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        self.weight = get(self.name).to(torch.float32).contiguous()
+        self.out_dtype = runtime.dtype
+
+    def forward(self, residual: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return K.layernorm_rows(residual, self.weight, self.eps, self.out_dtype, rows, self.normed_kind)
+
+    def forward_in_place(self, x: torch.Tensor) -> torch.Tensor:
+        """The fp32 rows ``x`` rewritten with their norm (a norm on the embedding: the stream stays fp32)."""
+        return K.layernorm_rows(x, self.weight, self.eps, torch.float32, None, self.normed_kind, in_place=True)
 
 
 class DynamicTanh(Norm):
@@ -99,3 +132,4 @@ RMSNorm.step_args = _rms_step_args
 
 NORMS.register("rmsnorm", RMSNorm)
 NORMS.register("dynamic_tanh", DynamicTanh)
+NORMS.register("layernorm", LayerNorm)
