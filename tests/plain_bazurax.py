@@ -183,3 +183,13 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layers_out
         if layers_out is not None:
             layers_out.append(x.clone())
     return layer_norm(x, w["final.norm"], eps) @ w["embed"].T
+
+
+def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    """n tokens, each the largest logit after the whole sequence so far (recomputed from the start every time)."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        t = int(forward(cfg, w, seq)[-1].argmax())
+        out.append(t)
+        seq.append(t)
+    return out
