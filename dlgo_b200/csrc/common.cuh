@@ -80,6 +80,11 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // step's first kernel starts.  That first kernel (the embedding) is launched WITHOUT the attribute
 // (launch_kernel_first), so it starts only after everything before it on the stream has completed;
 // every later kernel of the chain starts after it.
+// A pointer to anything that a kernel of the same step writes (activations, scratch, state, the residual) is NOT
+// declared __restrict__: the compiler treats loads through a const __restrict__ parameter as loads of memory that
+// never changes while the kernel runs, and memory behind any __restrict__ parameter as out of reach of the wait's
+// inline assembly, so it may issue such loads ahead of pdl_wait(), while the predecessor is still writing.
+// __restrict__ is for weights, tables and the step's own inputs only.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -54,7 +54,7 @@ __device__ __forceinline__ void row_stats(const float4 (&u)[NV], int d, int tid,
 
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
-add_normed_vec_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ w, T* __restrict__ act,
+add_normed_vec_kernel(float* x, float* y, const float* __restrict__ w, T* act,
                       int d, int kind, float eps, int clear_y) {
   constexpr int NV = 4;
   __shared__ float red[32];
@@ -99,7 +99,7 @@ add_normed_vec_kernel(float* __restrict__ x, float* __restrict__ y, const float*
 // any row length: the row is read again for every pass
 template <typename T>
 __global__ void __launch_bounds__(256)
-add_normed_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ w, T* __restrict__ act, int d,
+add_normed_kernel(float* x, float* y, const float* __restrict__ w, T* act, int d,
                   int kind, float eps, int clear_y) {
   __shared__ float red[32];
   pdl_launch_dependents();

@@ -16,10 +16,10 @@ namespace dlgo {
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
-__global__ void lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
+__global__ void lightning_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off,
                                       const int* __restrict__ tiles, const int* __restrict__ seq_slot,
-                                      const float* __restrict__ decay, float* __restrict__ state,
-                                      float* __restrict__ out, int ldo, int H, int dk, int dv, int dvc, int act) {
+                                      const float* __restrict__ decay, float* state,
+                                      float* out, int ldo, int H, int dk, int dv, int dvc, int act) {
   pdl_launch_dependents();
   extern __shared__ float smem[];
   // the block's columns [e0, e0 + n) of the state (columns are independent of one another)
@@ -70,7 +70,7 @@ __global__ void lightning_scan_kernel(const float* __restrict__ proj, int ld, in
 // its cosine and sine, in fp32); keys are then multiplied by `k_scale`.  A warp per (token, q or k head).
 constexpr int RS_WARPS = 4;
 __global__ void __launch_bounds__(RS_WARPS * 32)
-rotate_scale_kernel(float* __restrict__ proj, int ld, int q_off, int k_off, const float* __restrict__ freq, int rot,
+rotate_scale_kernel(float* proj, int ld, int q_off, int k_off, const float* __restrict__ freq, int rot,
                     const int* __restrict__ token_pos, int T, int H, int dk, float k_scale) {
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -104,10 +104,10 @@ rotate_scale_kernel(float* __restrict__ proj, int ld, int q_off, int k_off, cons
 // With DIRECT (one segment per sequence: decoding, short prompts) pass 2 runs alone and starts from S_in.
 template <int DK, bool LOCAL, bool DIRECT>
 __global__ void __launch_bounds__(128)
-lightning_segments_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
+lightning_segments_kernel(const float* proj, int ld, int q_off, int k_off, int v_off,
                           const int* __restrict__ tiles, int n_tiles, const int* __restrict__ seq_slot,
-                          const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ local,
-                          float* __restrict__ start_copy, float* __restrict__ out, int ldo, int H, int dv, int act) {
+                          const float* __restrict__ decay, float* state, float* local,
+                          float* start_copy, float* out, int ldo, int H, int dv, int act) {
   pdl_launch_dependents();
   __shared__ __align__(16) float qk[2][2 * DK];
   const int tile = blockIdx.x, h = blockIdx.y;

@@ -17,8 +17,8 @@ namespace dlgo {
 
 template <typename T, bool WARP_ROW>
 __global__ void __launch_bounds__(256)
-scaled_add_rmsnorm_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ ls,
-                          const float* __restrict__ w, T* __restrict__ act, int rows, int d, float skip, float eps,
+scaled_add_rmsnorm_kernel(float* x, float* y, const float* __restrict__ ls,
+                          const float* __restrict__ w, T* act, int rows, int d, float skip, float eps,
                           int clear_y) {
   __shared__ float red[32];
   pdl_launch_dependents();
@@ -68,8 +68,8 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
-scaled_add_rmsnorm_vec_kernel(float* __restrict__ x, float* __restrict__ y, const float* __restrict__ ls,
-                              const float* __restrict__ w, T* __restrict__ act, int d, float skip, float eps,
+scaled_add_rmsnorm_vec_kernel(float* x, float* y, const float* __restrict__ ls,
+                              const float* __restrict__ w, T* act, int d, float skip, float eps,
                               int clear_y) {
   constexpr int NV = 4;
   __shared__ float red[32];

@@ -208,8 +208,8 @@ __device__ __forceinline__ float gate_of(float g, int gate_act) {
 
 // out[t, :] = o[t, :] / sqrt(mean(o[t, :]^2) + eps) * w * gate(g[t, :]) * c;  o, g fp32 with row strides; w may be null
 template <typename TO>
-__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, int ldg,
-                                     const float* __restrict__ w, TO* __restrict__ out, int n, float eps, int gate_act,
+__global__ void gated_rmsnorm_kernel(const float* o, int ldo, const float* g, int ldg,
+                                     const float* __restrict__ w, TO* out, int n, float eps, int gate_act,
                                      float c) {
   pdl_launch_dependents();
   __shared__ float scratch[32];
@@ -232,8 +232,8 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, int ldo, const
 constexpr int GG_WARPS = 4;
 template <typename TO>
 __global__ void __launch_bounds__(GG_WARPS * 32)
-gated_groupnorm_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, int ldg,
-                       const float* __restrict__ w, TO* __restrict__ out, int T, int n, int group, float eps,
+gated_groupnorm_kernel(const float* o, int ldo, const float* g, int ldg,
+                       const float* __restrict__ w, TO* out, int T, int n, int group, float eps,
                        int gate_act, float c) {
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

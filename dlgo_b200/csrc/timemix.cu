@@ -25,10 +25,10 @@
 namespace dlgo {
 
 template <typename TO>
-__global__ void token_shift_mix_kernel(const float* __restrict__ x, const float* __restrict__ mu, int n_mix,
+__global__ void token_shift_mix_kernel(const float* x, const float* __restrict__ mu, int n_mix,
                                        const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
-                                       const float* __restrict__ state, long long state_ld, int prev_off,
-                                       TO* __restrict__ out, int T, int d) {
+                                       const float* state, long long state_ld, int prev_off,
+                                       TO* out, int T, int d) {
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int seq = token_seq[t];
@@ -47,17 +47,17 @@ __global__ void token_shift_mix_kernel(const float* __restrict__ x, const float*
 __device__ __forceinline__ float decay_of(float z, float w0) { return expf(-expf(z + w0)); }
 
 // the last input of a sequence's tokens of this step into its state row (the part of d that block `part` of `parts` owns)
-__device__ __forceinline__ void keep_last_input(const float* __restrict__ x, int d, int last_tok, float* st_prev, int part,
+__device__ __forceinline__ void keep_last_input(const float* x, int d, int last_tok, float* st_prev, int part,
                                                 int parts) {
   if (x == nullptr) return;
   for (int i = part * blockDim.x + threadIdx.x; i < d; i += parts * blockDim.x) st_prev[i] = x[(size_t)last_tok * d + i];
 }
 
-__global__ void wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
-                                const float* __restrict__ zw, int ld, const float* __restrict__ w0,
+__global__ void wkv_scan_kernel(const float* r, const float* k, const float* v, const float* zw, int ld,
+                                const float* __restrict__ w0,
                                 const float* __restrict__ u, const int* __restrict__ tiles,
-                                const int* __restrict__ seq_slot, float* __restrict__ state, long long state_ld,
-                                const float* __restrict__ x, int d, float* __restrict__ out, int H, int n, int dvc) {
+                                const int* __restrict__ seq_slot, float* state, long long state_ld, const float* x,
+                                int d, float* out, int H, int n, int dvc) {
   pdl_launch_dependents();
   extern __shared__ float smem[];
   const int e0 = blockIdx.z * dvc, nc = min(dvc, n - e0);
@@ -112,12 +112,11 @@ enum { WKV_DIRECT = 0, WKV_LOCAL = 1, WKV_CARRY = 2 };
 
 template <int DK, int MODE>
 __global__ void __launch_bounds__(128)
-wkv_segments_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
-                    const float* __restrict__ zw, int ld, const float* __restrict__ w0, const float* __restrict__ u,
+wkv_segments_kernel(const float* r, const float* k, const float* v, const float* zw, int ld,
+                    const float* __restrict__ w0, const float* __restrict__ u,
                     const int* __restrict__ tiles, int n_tiles, const int* __restrict__ seq_slot,
-                    float* __restrict__ state, long long state_ld, const float* __restrict__ x, int d,
-                    float* __restrict__ local, float* __restrict__ start_copy, float* __restrict__ decays,
-                    float* __restrict__ out, int H) {
+                    float* state, long long state_ld, const float* x, int d, float* local, float* start_copy,
+                    float* decays, float* out, int H) {
   pdl_launch_dependents();
   constexpr int dv = DK;
   __shared__ __align__(16) float rkw[2][3 * DK];

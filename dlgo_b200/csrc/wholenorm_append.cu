@@ -24,11 +24,11 @@ __device__ int g_wholenorm_append_error = 0;
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-wholenorm_append_kernel(float* __restrict__ proj, int ld, const float* __restrict__ w_q, const float* __restrict__ w_k,
+wholenorm_append_kernel(float* proj, int ld, const float* __restrict__ w_q, const float* __restrict__ w_k,
                         float eps, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                         const int* __restrict__ seq_slot, const int* __restrict__ page_table, int max_pages,
-                        T* __restrict__ kpages, T* __restrict__ vpages, T* __restrict__ q_out,
-                        float* __restrict__ gate_out, int Hq, int Hkv, int dk, int dv, int hd, int page_size,
+                        T* kpages, T* vpages, T* q_out,
+                        float* gate_out, int Hq, int Hkv, int dk, int dv, int hd, int page_size,
                         int has_gate, float gate_scale, int write_cache, int clear) {
   __shared__ float red[32];
   pdl_launch_dependents();
@@ -84,7 +84,7 @@ wholenorm_append_kernel(float* __restrict__ proj, int ld, const float* __restric
 // a[t, h, :] *= gate[t, h]   (a in the run's type, heads of hd numbers; the product is formed in fp32)
 template <typename T>
 __global__ void __launch_bounds__(256)
-scale_heads_kernel(T* __restrict__ a, const float* __restrict__ gate, long long total, int hd) {
+scale_heads_kernel(T* a, const float* gate, long long total, int hd) {
   pdl_launch_dependents();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
