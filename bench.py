@@ -386,6 +386,43 @@ def monolix_pair(size):
     return mono, llama
 
 
+# --only bazurax: the Bazurax design beside Llama at equal layer sizes (random weights)
+BAZURAX_SIZES = {
+    # width, heads / kv heads of the window attention and heads of the retention, head size, window, heads and head
+    # size of the time mixing, width of its decay projection, dense feed-forward, experts, chosen, expert width
+    "small": dict(width=1024, heads=16, kv=4, dim=64, window=512, tm_heads=16, tm_dim=64, rank=32, ff=2816,
+                  experts=16, top=2, eff=1408, rot=32, vocab=32000),
+    "1b": dict(width=2048, heads=16, kv=4, dim=128, window=1024, tm_heads=32, tm_dim=64, rank=64, ff=5632,
+               experts=32, top=4, eff=1408, rot=64, vocab=32000),
+    "3b": dict(width=3072, heads=24, kv=8, dim=128, window=1024, tm_heads=48, tm_dim=64, rank=96, ff=8192,
+               experts=32, top=4, eff=2048, rot=64, vocab=32000),
+}
+
+
+def bazurax_pair(size):
+    """(Bazurax config.json, Llama config.json): four layers, one of each pairing of mixer (retention; window
+    attention beside time mixing) and feed-forward (dense; experts whose chosen ones spend the dense one's FLOPs);
+    Llama with as many layers of the same width, heads, head size and dense feed-forward."""
+    z = BAZURAX_SIZES[size]
+    H, hd = z["heads"], z["dim"]
+    ret = {"heads": H, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** -(5 + 3 * i / H) for i in range(H)],
+           "rot": {"base": 10000.0, "dims": z["rot"]}}
+    par = {"left": {"heads": H, "kv_heads": z["kv"], "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                    "mask": {"size": z["window"]}},
+           "right": {"heads": z["tm_heads"], "dim": z["tm_dim"], "rank": z["rank"]},
+           "left_scale": 0.5, "right_scale": 0.5}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    baz = {"architecture": "Bazurax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+           "layers": [{"type": "retention", "mixer": ret, "mlp": dense}, {"type": "parallel", "mixer": par, "mlp": moe},
+                      {"type": "retention", "mixer": ret, "mlp": moe}, {"type": "parallel", "mixer": par, "mlp": dense}]}
+    llama = dict(architectures=["LlamaForCausalLM"], hidden_size=z["width"], num_hidden_layers=4,
+                 intermediate_size=z["ff"], num_attention_heads=H, num_key_value_heads=z["kv"], head_dim=hd,
+                 vocab_size=z["vocab"], rope_theta=500000.0, rope_scaling=None, rms_norm_eps=1e-5,
+                 max_position_embeddings=8192, tie_word_embeddings=False)
+    return baz, llama
+
+
 def dedutar_compare(size, batch, steps, warmup, prefill_tokens, profile, design="dedutar"):
     """Prefill and decode throughput of both models, and (with `profile`) the time per kernel entry point of
     one prompt step and of decode steps launched one by one."""
@@ -396,7 +433,8 @@ def dedutar_compare(size, batch, steps, warmup, prefill_tokens, profile, design=
     from dlgo_b200.weights import write_random_model
     out = {"only": design, "size": size, "batch": batch, "prefill_tokens": prefill_tokens, "dtype": "bf16",
            "data": "synthetic", "models": {}}
-    for name, cfg in zip((design, "llama"), monolix_pair(size) if design == "monolix" else dedutar_pair(size)):
+    pair = {"monolix": monolix_pair, "dedutar": dedutar_pair, "bazurax": bazurax_pair}[design](size)
+    for name, cfg in zip((design, "llama"), pair):
         tmp = tempfile.mkdtemp(prefix=f"bench_{name}_")
         try:
             write_random_model(config_from_dict(cfg), 2, tmp, device="cuda")
@@ -492,12 +530,13 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="--only prefill: tokens of the prompt")
     ap.add_argument("--prefill-batch", type=int, default=0,
                     help="--only prefill: a packed batch of that many prompts with lengths from --prompt-range")
-    ap.add_argument("--only", choices=["decode", "prefill", "phases", "sampled", "dedutar", "monolix"],
+    ap.add_argument("--only", choices=["decode", "prefill", "phases", "sampled", "dedutar", "monolix", "bazurax"],
                     help="run one small workload (for profiling) and stop; phases: see phase_stamps(); dedutar, "
-                         "monolix: prefill and decode of that design beside Llama at equal layer sizes")
+                         "monolix, bazurax: prefill and decode of that design beside Llama at equal layer sizes")
+    ap.add_argument("--bazurax-size", default="1b", choices=sorted(BAZURAX_SIZES), help="--only bazurax: layer sizes")
     ap.add_argument("--monolix-size", default="1b", choices=sorted(MONOLIX_SIZES), help="--only monolix: layer sizes")
     ap.add_argument("--dedutar-size", default="1b", choices=sorted(DEDUTAR_SIZES), help="--only dedutar: layer sizes")
-    ap.add_argument("--kernels", action="store_true", help="--only dedutar / monolix: also the time per kernel entry point")
+    ap.add_argument("--kernels", action="store_true", help="--only dedutar / monolix / bazurax: also the time per kernel entry point")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode kernels one by one (for profiling)")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -520,6 +559,10 @@ def main() -> int:
     if a.only == "monolix":
         print(json.dumps(dedutar_compare(a.monolix_size, a.batch, a.steps, warmup, a.prefill_tokens, a.kernels,
                                          design="monolix")))
+        return 0
+    if a.only == "bazurax":
+        print(json.dumps(dedutar_compare(a.bazurax_size, a.batch, a.steps, warmup, a.prefill_tokens, a.kernels,
+                                         design="bazurax")))
         return 0
     pk = peaks()
     global PROMPT_LEN, PROMPT_RANGE
