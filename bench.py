@@ -34,7 +34,7 @@ MODEL = dict(
     rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=8192),
     rms_norm_eps=1e-5, max_position_embeddings=131072, tie_word_embeddings=True)
-# further shapes for extra measurements (`--shape`); the contract's line is measured at the default
+# further shapes for extra measurements (`--shape`); the headline line is measured at the default
 SHAPES = {
     "1b": {},
     "3b": dict(hidden_size=3072, num_hidden_layers=28, intermediate_size=8192, num_attention_heads=24,
@@ -522,7 +522,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "plain-cpu"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes (default: the contract's Llama 3.2 1B)")
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes (default: the headline's Llama 3.2 1B)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
     ap.add_argument("--prompt-len", type=int, default=0, help="fixed prompt length instead of uniform[128,1024]")
     ap.add_argument("--prompt-range", default="", help="LO,HI: prompt lengths uniform in [LO, HI] (default 128,1024)")

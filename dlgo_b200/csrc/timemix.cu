@@ -110,20 +110,33 @@ __global__ void wkv_scan_kernel(const float* r, const float* k, const float* v, 
 
 enum { WKV_DIRECT = 0, WKV_LOCAL = 1, WKV_CARRY = 2 };
 
+// 16 bytes from global to shared memory without passing through registers; groups of copies are waited for in order
+__device__ __forceinline__ void copy16_async(float* dst_shared, const float* src) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(dst_shared);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int WKV_CHUNK = 8;     // tokens that are fetched together, one chunk ahead of the products
+
+// A block of DK threads per (segment, head): thread e keeps column e of the state in registers and owns decay
+// channel e.  A token's r | k | z | v (4 DK numbers) come in chunks of WKV_CHUNK tokens through a ring of two
+// shared-memory buffers filled by asynchronous copies, so that a token's products never wait for memory; when a
+// chunk has landed its z become decays in place (thread e: channel e of every token).
 template <int DK, int MODE>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(DK)
 wkv_segments_kernel(const float* r, const float* k, const float* v, const float* zw, int ld,
                     const float* __restrict__ w0, const float* __restrict__ u,
                     const int* __restrict__ tiles, int n_tiles, const int* __restrict__ seq_slot,
                     float* state, long long state_ld, const float* x, int d, float* local, float* start_copy,
                     float* decays, float* out, int H) {
   pdl_launch_dependents();
-  constexpr int dv = DK;
-  __shared__ __align__(16) float rkw[2][3 * DK];
+  constexpr int dv = DK, CH = WKV_CHUNK, ROW = 4 * DK, PIECES = DK / 4;
+  __shared__ __align__(16) float ring[2][CH * ROW];
   __shared__ __align__(16) float us[DK];
   const int tile = blockIdx.x, h = blockIdx.y;
-  const int e = blockIdx.z * blockDim.x + threadIdx.x;          // this thread's column of the state
-  const bool live = e < dv;
+  const int e = threadIdx.x;                                     // this thread's column of the state, and its channel
   const int seq = tiles[tile * 3 + 0], first = tiles[tile * 3 + 1], count = tiles[tile * 3 + 2];
   const int slot = seq_slot[seq];
   int t0 = tile;                                                 // the sequence's first segment
@@ -131,121 +144,93 @@ wkv_segments_kernel(const float* r, const float* k, const float* v, const float*
   const bool last = tile + 1 == n_tiles || tiles[(tile + 1) * 3] != seq;
   float* st = state + (size_t)slot * state_ld + (size_t)h * DK * dv;
   const size_t seg_elems = (size_t)H * DK * dv;
-  for (int i = threadIdx.x; i < DK; i += blockDim.x) us[i] = u[h * DK + i];
-  // r, k and the decay of a token are 3 DK numbers; number i of them is fetched by thread i % 128 as its part
-  // i / 128.  With DK = 32, 64 or 128 the DK decay numbers fall into ONE part, so a thread meets at most one decay
-  // channel, the same for every token: it keeps that channel's w0 and (pass 1) the product of the channel's decays.
-  constexpr int PER_T = (3 * DK + 127) / 128;
-  int my_channel = -1;
-#pragma unroll
-  for (int j = 0; j < PER_T; ++j) {
-    const int i = threadIdx.x + j * 128;
-    if (i >= 2 * DK && i < 3 * DK) my_channel = i - 2 * DK;
-  }
-  const float w0_mine = my_channel >= 0 ? w0[h * DK + my_channel] : 0.f;
+  us[e] = u[h * DK + e];
+  const float w0_mine = w0[h * DK + e];
   pdl_wait();
+  auto load_chunk = [&](int c, float* buf) {
+    const int tok0 = first + c * CH, nt = min(CH, count - c * CH);
+    for (int i = threadIdx.x; i < nt * 4 * PIECES; i += DK) {
+      const int t = i / (4 * PIECES), a = (i / PIECES) & 3, p = i % PIECES;
+      const float* src = a == 0 ? r : (a == 1 ? k : (a == 2 ? zw : v));
+      copy16_async(buf + t * ROW + a * DK + p * 4, src + (size_t)(tok0 + t) * ld + (size_t)h * DK + p * 4);
+    }
+    copies_commit();
+  };
+  const int n_chunks = (count + CH - 1) / CH;
+  load_chunk(0, ring[0]);
   float S[DK];
   if (MODE == WKV_LOCAL) {
 #pragma unroll
     for (int i = 0; i < DK; ++i) S[i] = 0.f;
-    if (tile == t0 && live)
+    if (tile == t0)
       for (int i = 0; i < DK; ++i) start_copy[(size_t)tile * seg_elems + ((size_t)h * DK + i) * dv + e] = st[(size_t)i * dv + e];
   } else if (MODE == WKV_DIRECT) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i) S[i] = live ? st[(size_t)i * dv + e] : 0.f;
+    for (int i = 0; i < DK; ++i) S[i] = st[(size_t)i * dv + e];
   } else {
 #pragma unroll
-    for (int i = 0; i < DK; ++i)
-      S[i] = live ? start_copy[(size_t)t0 * seg_elems + ((size_t)h * DK + i) * dv + e] : 0.f;
+    for (int i = 0; i < DK; ++i) S[i] = start_copy[(size_t)t0 * seg_elems + ((size_t)h * DK + i) * dv + e];
     for (int j = t0; j < tile; ++j) {
       const float* L = local + (size_t)j * seg_elems + (size_t)h * DK * dv;
       const float* P = decays + ((size_t)j * H + h) * DK;
-      if (live) {
 #pragma unroll
-        for (int i = 0; i < DK; ++i) S[i] = fmaf(P[i], S[i], L[(size_t)i * dv + e]);
-      }
+      for (int i = 0; i < DK; ++i) S[i] = fmaf(P[i], S[i], L[(size_t)i * dv + e]);
     }
   }
-  // fetched into registers one token ahead and put into shared memory behind the current token's products
-  float raw[PER_T];
-  auto fetch = [&](int tok) {
-    const size_t row = (size_t)tok * ld + (size_t)h * DK;
-#pragma unroll
-    for (int j = 0; j < PER_T; ++j) {
-      const int i = threadIdx.x + j * 128;
-      float val = 0.f;
-      if (i < DK) val = r[row + i];
-      else if (i < 2 * DK) val = k[row + i - DK];
-      else if (i < 3 * DK) val = zw[row + i - 2 * DK];
-      raw[j] = val;
+  float prod = 1.0f;                                             // product of this segment's decays in channel e
+  for (int c = 0; c < n_chunks; ++c) {
+    float* buf = ring[c & 1];
+    if (c + 1 < n_chunks) {
+      load_chunk(c + 1, ring[(c + 1) & 1]);                      // (its last readers passed the barrier that ended chunk c - 1)
+      copies_wait<1>();
+    } else {
+      copies_wait<0>();
     }
-  };
-  float prod = 1.0f;                                             // product of this segment's decays in my_channel
-  auto put = [&](float* buf) {
-#pragma unroll
-    for (int j = 0; j < PER_T; ++j) {
-      const int i = threadIdx.x + j * 128;
-      if (i >= 2 * DK && i < 3 * DK) {
-        const float w = decay_of(raw[j], w0_mine);
-        buf[i] = w;
-        if (MODE == WKV_LOCAL) prod *= w;
-      } else if (i < 2 * DK) {
-        buf[i] = raw[j];
-      }
-    }
-  };
-  fetch(first);
-  put(rkw[0]);
-  const float* vcol = v + (size_t)h * DK + (live ? e : 0);
-  float v_next = vcol[(size_t)first * ld];
-  __syncthreads();
-  for (int n = 0; n < count; ++n) {
-    const float* cur = rkw[n & 1];
-    const float val = live ? v_next : 0.f;
-    const bool more = n + 1 < count;
-    if (more) {
-      v_next = vcol[(size_t)(first + n + 1) * ld];
-      fetch(first + n + 1);
-    }
-    float o = 0.f;
-#pragma unroll
-    for (int i = 0; i < DK; i += 4) {
-      const float4 k4 = *reinterpret_cast<const float4*>(cur + DK + i);
-      const float4 w4 = *reinterpret_cast<const float4*>(cur + 2 * DK + i);
-      const float kv0 = k4.x * val, kv1 = k4.y * val, kv2 = k4.z * val, kv3 = k4.w * val;
-      if (MODE != WKV_LOCAL) {
-        const float4 r4 = *reinterpret_cast<const float4*>(cur + i);
-        const float4 u4 = *reinterpret_cast<const float4*>(us + i);
-        o = fmaf(r4.x, fmaf(u4.x, kv0, S[i]), o);
-        o = fmaf(r4.y, fmaf(u4.y, kv1, S[i + 1]), o);
-        o = fmaf(r4.z, fmaf(u4.z, kv2, S[i + 2]), o);
-        o = fmaf(r4.w, fmaf(u4.w, kv3, S[i + 3]), o);
-      }
-      S[i] = fmaf(w4.x, S[i], kv0);
-      S[i + 1] = fmaf(w4.y, S[i + 1], kv1);
-      S[i + 2] = fmaf(w4.z, S[i + 2], kv2);
-      S[i + 3] = fmaf(w4.w, S[i + 3], kv3);
-    }
-    if (more) put(rkw[(n + 1) & 1]);
-    if (MODE != WKV_LOCAL && live) out[(size_t)(first + n) * ld + h * DK + e] = o;
     __syncthreads();
+    const int nt = min(CH, count - c * CH);
+    for (int t = 0; t < nt; ++t) {
+      const float w = decay_of(buf[t * ROW + 2 * DK + e], w0_mine);
+      buf[t * ROW + 2 * DK + e] = w;
+      if (MODE == WKV_LOCAL) prod *= w;
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      const float* cur = buf + t * ROW;
+      const float val = cur[3 * DK + e];
+      float o0 = 0.f, o1 = 0.f;                                   // two chains of sums; more of them cost registers that a 128-wide state needs
+#pragma unroll
+      for (int i = 0; i < DK; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(cur + DK + i);
+        const float4 w4 = *reinterpret_cast<const float4*>(cur + 2 * DK + i);
+        const float kv0 = k4.x * val, kv1 = k4.y * val, kv2 = k4.z * val, kv3 = k4.w * val;
+        if (MODE != WKV_LOCAL) {
+          const float4 r4 = *reinterpret_cast<const float4*>(cur + i);
+          const float4 u4 = *reinterpret_cast<const float4*>(us + i);
+          o0 = fmaf(r4.x, fmaf(u4.x, kv0, S[i]), o0);
+          o1 = fmaf(r4.y, fmaf(u4.y, kv1, S[i + 1]), o1);
+          o0 = fmaf(r4.z, fmaf(u4.z, kv2, S[i + 2]), o0);
+          o1 = fmaf(r4.w, fmaf(u4.w, kv3, S[i + 3]), o1);
+        }
+        S[i] = fmaf(w4.x, S[i], kv0);
+        S[i + 1] = fmaf(w4.y, S[i + 1], kv1);
+        S[i + 2] = fmaf(w4.z, S[i + 2], kv2);
+        S[i + 3] = fmaf(w4.w, S[i + 3], kv3);
+      }
+      if (MODE != WKV_LOCAL) out[(size_t)(first + c * CH + t) * ld + h * DK + e] = o0 + o1;
+    }
+    __syncthreads();                                             // the buffer is free for the chunk after next
   }
   if (MODE == WKV_LOCAL) {
-    if (blockIdx.z == 0 && my_channel >= 0) decays[((size_t)tile * H + h) * DK + my_channel] = prod;
-    if (live) {
-      float* L = local + (size_t)tile * seg_elems + (size_t)h * DK * dv;
+    decays[((size_t)tile * H + h) * DK + e] = prod;
+    float* L = local + (size_t)tile * seg_elems + (size_t)h * DK * dv;
 #pragma unroll
-      for (int i = 0; i < DK; ++i) L[(size_t)i * dv + e] = S[i];
-    }
+    for (int i = 0; i < DK; ++i) L[(size_t)i * dv + e] = S[i];
     return;
   }
   if (last) {
-    if (live) {
 #pragma unroll
-      for (int i = 0; i < DK; ++i) st[(size_t)i * dv + e] = S[i];
-    }
-    if (blockIdx.z == 0)
-      keep_last_input(x, d, first + count - 1, state + (size_t)slot * state_ld + (size_t)H * DK * dv, h, H);
+    for (int i = 0; i < DK; ++i) st[(size_t)i * dv + e] = S[i];
+    keep_last_input(x, d, first + count - 1, state + (size_t)slot * state_ld + (size_t)H * DK * dv, h, H);
   }
 }
 
@@ -254,7 +239,7 @@ static int launch_wkv_segments(const float* r, const float* k, const float* v, c
                                const float* u, const int* tiles, int n_tiles, int direct, const int* seq_slot,
                                float* state, long long state_ld, const float* x, int d, float* scratch, float* out,
                                int H, cudaStream_t stream) {
-  const dim3 grid(n_tiles, H, (DK + 127) / 128), block(128);
+  const dim3 grid(n_tiles, H), block(DK);
   const size_t seg = (size_t)n_tiles * H * DK * DK;
   float* local = scratch;
   float* start_copy = scratch ? scratch + seg : nullptr;
@@ -309,6 +294,8 @@ DLGO_EXPORT int dlgo_wkv_segments(const float* r, const float* k, const float* v
                                   float* scratch, float* out, int H, int n, cudaStream_t stream) {
   if (n_tiles <= 0) return DLGO_OK;
   if (H <= 0 || H > 65535) return DLGO_ERR_SIZE;
+  // rows are fetched in 16-byte pieces
+  if ((((size_t)r | (size_t)k | (size_t)v | (size_t)zw) & 15) || (ld & 3)) return DLGO_ERR_SIZE;
 #define WKV_ARGS r, k, v, zw, ld, w0, u, tiles, n_tiles, direct, seq_slot, state, state_ld, x, d, scratch, out, H, stream
   if (n == 32) return launch_wkv_segments<32>(WKV_ARGS);
   if (n == 64) return launch_wkv_segments<64>(WKV_ARGS);

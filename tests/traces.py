@@ -12,7 +12,7 @@ import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# a trace step also records, for the checker, which (request, position) each wanted row is
+# a trace step also records, for the test that compares, which (request, position) each wanted row is
 Step = dict
 
 
