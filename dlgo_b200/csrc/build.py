@@ -50,7 +50,8 @@ LIBRARIES: Dict[str, List[str]] = {
     "timemix": ["timemix.cu"],
     "wholenorm_append": ["wholenorm_append.cu"],
 }
-_HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "attention_decode_tiles.cuh", "tcgen05.cuh"]
+_HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "attention_decode_tiles.cuh", "tcgen05.cuh",
+            "async_copy.cuh"]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

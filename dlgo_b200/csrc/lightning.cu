@@ -11,6 +11,7 @@
 // memory while the block walks the sequence's tokens of this step in order.  The projections arrive as fp32 rows [q | k | v | ...]; activation,
 // decay, state and output are fp32.
 #include "common.cuh"
+#include "async_copy.cuh"
 
 namespace dlgo {
 
@@ -102,16 +103,24 @@ rotate_scale_kernel(float* proj, int ld, int q_off, int k_off, const float* __re
 //   pass 2:         segment i starts from  lambda^(n_0 + .. + n_(i-1)) S_in + sum_(j<i) lambda^(n_(j+1) + .. + n_(i-1)) L_j,
 //                   walks its tokens and writes their outputs; the last segment stores the sequence's new state
 // With DIRECT (one segment per sequence: decoding, short prompts) pass 2 runs alone and starts from S_in.
+// A token's q | k (2 DK numbers) and the block's up to 128 value columns come in chunks of SEG_CHUNK tokens through
+// a ring of two shared-memory buffers filled by asynchronous copies, one chunk ahead of the products, so that a
+// token's products never wait for memory (`vec`: every piece starts on a 16-byte boundary; else 4-byte copies).
+constexpr int SEG_CHUNK = 8;
+
 template <int DK, bool LOCAL, bool DIRECT>
 __global__ void __launch_bounds__(128)
 lightning_segments_kernel(const float* proj, int ld, int q_off, int k_off, int v_off,
                           const int* __restrict__ tiles, int n_tiles, const int* __restrict__ seq_slot,
                           const float* __restrict__ decay, float* state, float* local,
-                          float* start_copy, float* out, int ldo, int H, int dv, int act) {
+                          float* start_copy, float* out, int ldo, int H, int dv, int act, int vec) {
   pdl_launch_dependents();
-  __shared__ __align__(16) float qk[2][2 * DK];
+  constexpr int CH = SEG_CHUNK, ROW = 2 * DK + 128;
+  __shared__ __align__(16) float ring[2][CH * ROW];
   const int tile = blockIdx.x, h = blockIdx.y;
-  const int e = blockIdx.z * blockDim.x + threadIdx.x;          // this thread's column of the state
+  const int e0 = blockIdx.z * 128;                               // the block's first column of the state
+  const int e = e0 + threadIdx.x;                                // this thread's column
+  const int nv = min(128, dv - e0);
   const bool live = e < dv;
   const int seq = tiles[tile * 3 + 0], first = tiles[tile * 3 + 1], count = tiles[tile * 3 + 2];
   const int slot = seq_slot[seq];
@@ -122,12 +131,33 @@ lightning_segments_kernel(const float* proj, int ld, int q_off, int k_off, int v
   float* st = state + ((size_t)slot * H + h) * DK * dv;
   const size_t seg_elems = (size_t)H * DK * dv;
   pdl_wait();
+  auto load_chunk = [&](int c, float* buf) {
+    const int tok0 = first + c * CH, nt = min(CH, count - c * CH);
+    // a row of the buffer: q, k, then the block's value columns; piece p of a row lands at the same place p
+    const int unit = vec ? 4 : 1, per = (2 * DK + nv) / unit, nq = DK / unit;
+    for (int i = threadIdx.x; i < nt * per; i += 128) {
+      const int t = i / per, p = i - t * per;
+      const float* row = proj + (size_t)(tok0 + t) * ld;
+      const float* src = p < nq ? row + q_off + h * DK + p * unit
+                       : p < 2 * nq ? row + k_off + h * DK + (p - nq) * unit
+                                    : row + v_off + h * dv + e0 + (p - 2 * nq) * unit;
+      if (vec) copy16_async(buf + t * ROW + p * 4, src);
+      else copy4_async(buf + t * ROW + p, src);
+    }
+    copies_commit();
+  };
+  const int n_chunks = (count + CH - 1) / CH;
+  load_chunk(0, ring[0]);
   float S[DK];
   if (LOCAL) {
+    if (tile == t0 && live) {                                    // (all loads first: the copy's stores do not wait for them one by one)
+#pragma unroll
+      for (int i = 0; i < DK; ++i) S[i] = st[(size_t)i * dv + e];
+#pragma unroll
+      for (int i = 0; i < DK; ++i) start_copy[(size_t)tile * seg_elems + ((size_t)h * DK + i) * dv + e] = S[i];
+    }
 #pragma unroll
     for (int i = 0; i < DK; ++i) S[i] = 0.f;
-    if (tile == t0 && live)
-      for (int i = 0; i < DK; ++i) start_copy[(size_t)tile * seg_elems + ((size_t)h * DK + i) * dv + e] = st[(size_t)i * dv + e];
   } else if (DIRECT) {
 #pragma unroll
     for (int i = 0; i < DK; ++i) S[i] = live ? st[(size_t)i * dv + e] : 0.f;
@@ -149,57 +179,45 @@ lightning_segments_kernel(const float* proj, int ld, int q_off, int k_off, int v
       }
     }
   }
-  // q and k of a token: 2 DK numbers, fetched by the block's threads into registers one token ahead and put
-  // into shared memory (through silu) behind the current token's products
-  constexpr int PER_T = (2 * DK + 127) / 128;                    // (blocks have 128 threads)
-  float raw[PER_T];
-  auto fetch = [&](int tok) {
-    const float* row = proj + (size_t)tok * ld;
-#pragma unroll
-    for (int j = 0; j < PER_T; ++j) {
-      const int i = threadIdx.x + j * blockDim.x;
-      raw[j] = i < 2 * DK ? row[i < DK ? q_off + h * DK + i : k_off + h * DK + (i - DK)] : 0.f;
+  for (int c = 0; c < n_chunks; ++c) {
+    float* buf = ring[c & 1];
+    if (c + 1 < n_chunks) {
+      load_chunk(c + 1, ring[(c + 1) & 1]);                      // (its last readers passed the barrier that ended chunk c - 1)
+      copies_wait<1>();
+    } else {
+      copies_wait<0>();
     }
-  };
-  auto put = [&](float* buf) {
-#pragma unroll
-    for (int j = 0; j < PER_T; ++j) {
-      const int i = threadIdx.x + j * blockDim.x;
-      if (i < 2 * DK) buf[i] = act ? silu_f(raw[j]) : raw[j];
-    }
-  };
-  fetch(first);
-  put(qk[0]);
-  const float* vcol = proj + v_off + h * dv + (live ? e : 0);
-  float v_raw = vcol[(size_t)first * ld];
-  __syncthreads();
-  for (int n = 0; n < count; ++n) {
-    const float* cur = qk[n & 1];
-    const float v = live ? (act ? silu_f(v_raw) : v_raw) : 0.f;
-    const bool more = n + 1 < count;
-    if (more) {
-      v_raw = vcol[(size_t)(first + n + 1) * ld];
-      fetch(first + n + 1);
-    }
-    float o = 0.f;
-#pragma unroll
-    for (int i = 0; i < DK; i += 4) {
-      const float4 k4 = *reinterpret_cast<const float4*>(cur + DK + i);
-      S[i] = fmaf(lam, S[i], k4.x * v);
-      S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
-      S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
-      S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
-      if (!LOCAL) {
-        const float4 q4 = *reinterpret_cast<const float4*>(cur + i);
-        o = fmaf(S[i], q4.x, o);
-        o = fmaf(S[i + 1], q4.y, o);
-        o = fmaf(S[i + 2], q4.z, o);
-        o = fmaf(S[i + 3], q4.w, o);
-      }
-    }
-    if (more) put(qk[(n + 1) & 1]);
-    if (!LOCAL && live) out[(size_t)(first + n) * ldo + h * dv + e] = o;
     __syncthreads();
+    const int nt = min(CH, count - c * CH);
+    if (act) {                                                   // silu on q, k and v where they landed
+      for (int i = threadIdx.x; i < nt * ROW; i += 128) {
+        const int p = i % ROW;
+        if (p < 2 * DK + nv) buf[i] = silu_f(buf[i]);
+      }
+      __syncthreads();
+    }
+    for (int t = 0; t < nt; ++t) {
+      const float* cur = buf + t * ROW;
+      const float v = live ? cur[2 * DK + threadIdx.x] : 0.f;
+      float o0 = 0.f, o1 = 0.f;                                  // two chains of sums
+#pragma unroll
+      for (int i = 0; i < DK; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(cur + DK + i);
+        S[i] = fmaf(lam, S[i], k4.x * v);
+        S[i + 1] = fmaf(lam, S[i + 1], k4.y * v);
+        S[i + 2] = fmaf(lam, S[i + 2], k4.z * v);
+        S[i + 3] = fmaf(lam, S[i + 3], k4.w * v);
+        if (!LOCAL) {
+          const float4 q4 = *reinterpret_cast<const float4*>(cur + i);
+          o0 = fmaf(S[i], q4.x, o0);
+          o1 = fmaf(S[i + 1], q4.y, o1);
+          o0 = fmaf(S[i + 2], q4.z, o0);
+          o1 = fmaf(S[i + 3], q4.w, o1);
+        }
+      }
+      if (!LOCAL && live) out[(size_t)(first + c * CH + t) * ldo + h * dv + e] = o0 + o1;
+    }
+    __syncthreads();                                             // the buffer is free for the chunk after next
   }
   if (!live) return;
   if (LOCAL) {
@@ -219,18 +237,20 @@ static int launch_segments(const float* proj, int ld, int q_off, int k_off, int 
   const dim3 grid(n_tiles, H, (dv + 127) / 128), block(128);
   float* local = scratch;
   float* start_copy = scratch ? scratch + (size_t)n_tiles * H * DK * dv : nullptr;
+  // whether every piece of a row that is copied starts on a 16-byte boundary
+  const int vec = ((size_t)proj & 15) == 0 && ((ld | q_off | k_off | v_off | dv) & 3) == 0;
   if (direct) {
     launch_kernel(lightning_segments_kernel<DK, false, true>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off,
-                  tiles, n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv, act);
+                  tiles, n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv, act, vec);
     return launch_status();
   }
   if (!scratch) return DLGO_ERR_SIZE;
   launch_kernel(lightning_segments_kernel<DK, true, false>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off, tiles,
-                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv, act);
+                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv, act, vec);
   int st = launch_status();
   if (st != DLGO_OK) return st;
   launch_kernel(lightning_segments_kernel<DK, false, false>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off, tiles,
-                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv, act);
+                n_tiles, seq_slot, decay, state, local, start_copy, out, ldo, H, dv, act, vec);
   return launch_status();
 }
 

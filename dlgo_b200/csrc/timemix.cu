@@ -21,6 +21,7 @@
 //                  With one segment per sequence (decoding, short prompts) pass 2 runs alone from the stored state.
 // Decays, exponentials, state and outputs are fp32 in every precision.
 #include "common.cuh"
+#include "async_copy.cuh"
 
 namespace dlgo {
 
@@ -110,14 +111,6 @@ __global__ void wkv_scan_kernel(const float* r, const float* k, const float* v, 
 
 enum { WKV_DIRECT = 0, WKV_LOCAL = 1, WKV_CARRY = 2 };
 
-// 16 bytes from global to shared memory without passing through registers; groups of copies are waited for in order
-__device__ __forceinline__ void copy16_async(float* dst_shared, const float* src) {
-  const unsigned dst = (unsigned)__cvta_generic_to_shared(dst_shared);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 constexpr int WKV_CHUNK = 8;     // tokens that are fetched together, one chunk ahead of the products
 
 // A block of DK threads per (segment, head): thread e keeps column e of the state in registers and owns decay
@@ -160,10 +153,14 @@ wkv_segments_kernel(const float* r, const float* k, const float* v, const float*
   load_chunk(0, ring[0]);
   float S[DK];
   if (MODE == WKV_LOCAL) {
+    if (tile == t0) {                                            // (all loads first: the copy's stores do not wait for them one by one)
+#pragma unroll
+      for (int i = 0; i < DK; ++i) S[i] = st[(size_t)i * dv + e];
+#pragma unroll
+      for (int i = 0; i < DK; ++i) start_copy[(size_t)tile * seg_elems + ((size_t)h * DK + i) * dv + e] = S[i];
+    }
 #pragma unroll
     for (int i = 0; i < DK; ++i) S[i] = 0.f;
-    if (tile == t0)
-      for (int i = 0; i < DK; ++i) start_copy[(size_t)tile * seg_elems + ((size_t)h * DK + i) * dv + e] = st[(size_t)i * dv + e];
   } else if (MODE == WKV_DIRECT) {
 #pragma unroll
     for (int i = 0; i < DK; ++i) S[i] = st[(size_t)i * dv + e];

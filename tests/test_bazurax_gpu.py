@@ -213,7 +213,8 @@ def check_model(cfg, w, dtype, what, n=150, start=70, seed=6):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H, dk, dv, rot", [(3, 24, 16, 12), (1, 40, 24, 40), (2, 32, 40, 0), (2, 64, 32, 32), (1, 128, 64, 64),
-                                            (4, 16, 16, 8), (2, 64, 100, 64), (5, 6, 2, 2)])
+                                            (4, 16, 16, 8), (2, 64, 100, 64), (5, 6, 2, 2),
+                                            (2, 32, 30, 16), (1, 64, 130, 32), (1, 32, 136, 0)])
 def test_retention_alone(H, dk, dv, rot, dtype):
     decay = [1.0 - 2.0 ** -(2 + i) for i in range(H)]
     cfg = one_layer("retention", ret(H, dk, dv, decay, rot, 700.0))
