@@ -297,17 +297,19 @@ __global__ void add_rmsnorm_cluster_kernel(float* __restrict__ x, const float* _
 }
 
 // ------------------------------------------------------------------- SwiGLU
-// in: [T, 2F] with the gate in columns [0, F) and the up projection in [F, 2F).
+// in: [T, 2F]: blocks of `block` gate columns, each followed by its `block` up columns (block = F: the gate in
+// columns [0, F) and the up projection in [F, 2F)).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int F, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int F, int block, size_t total) {
   pdl_launch_dependents();
   pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   size_t t = i / F;
   int c = (int)(i - t * F);
-  float g = to_float(in[t * 2 * F + c]);
-  float u = to_float(in[t * 2 * F + F + c]);
+  const size_t at = t * 2 * F + (size_t)(c / block) * 2 * block + c % block;
+  float g = to_float(in[at]);
+  float u = to_float(in[at + block]);
   float h = g / (1.0f + expf(-g)) * u;
   out[i] = from_float<T>(h);
 }
@@ -366,20 +368,30 @@ DLGO_EXPORT int dlgo_rmsnorm(const float* x, const float* w, void* out, int out_
 }
 
 // in[T, 2F], out[T, F], same element type
-DLGO_EXPORT int dlgo_swiglu(const void* in, void* out, int dtype, int T, int F, cudaStream_t stream) {
+static int launch_swiglu(const void* in, void* out, int dtype, int T, int F, int block, cudaStream_t stream) {
   if (T <= 0) return DLGO_OK;
-  if (F <= 0) return DLGO_ERR_SIZE;
+  if (F <= 0 || block <= 0 || F % block != 0) return DLGO_ERR_SIZE;
   const size_t total = (size_t)T * F;
   const int threads = 256;
   const unsigned blocks = (unsigned)((total + threads - 1) / threads);
   if (dtype == DLGO_F32)
-    launch_kernel(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, F, total);
+    launch_kernel(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, F, block,
+                  total);
   else if (dtype == DLGO_BF16)
-    launch_kernel(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, F,
-                                                                 total);
+    launch_kernel(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in,
+                  (__nv_bfloat16*)out, F, block, total);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();
+}
+
+DLGO_EXPORT int dlgo_swiglu(const void* in, void* out, int dtype, int T, int F, cudaStream_t stream) {
+  return launch_swiglu(in, out, dtype, T, F, F, stream);
+}
+
+// gate and up columns in blocks of `block` (a divisor of F)
+DLGO_EXPORT int dlgo_swiglu_blocks(const void* in, void* out, int dtype, int T, int F, int block, cudaStream_t stream) {
+  return launch_swiglu(in, out, dtype, T, F, block, stream);
 }
 
 // x[*, d] f32 (updated in place), parts[S][*, d] f32 (slice stride part_stride floats), w[d] f32 or null,

@@ -158,16 +158,23 @@ def add_rmsnorm(x: torch.Tensor, parts: torch.Tensor, w: Optional[torch.Tensor],
     return out
 
 
-def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """[T, 2F] (gate | up) -> [T, F]."""
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, block: Optional[int] = None) -> torch.Tensor:
+    """[T, 2F] (gate | up) -> [T, F].  ``block``: gate and up columns alternate in blocks of this many columns
+    (a divisor of F) instead of two halves."""
     _need(gate_up, None, "gate_up")
     T, F2 = gate_up.shape
     F = F2 // 2
     if out is None:
         out = torch.empty((T, F), dtype=gate_up.dtype, device=gate_up.device)
     _need(out, gate_up.dtype, "out")
-    st = _lib("elementwise").dlgo_swiglu(_ptr(gate_up), _ptr(out), _i(dtype_code(gate_up.dtype)), _i(T), _i(F),
-                                         _stream())
+    if block is None or block == F:
+        st = _lib("elementwise").dlgo_swiglu(_ptr(gate_up), _ptr(out), _i(dtype_code(gate_up.dtype)), _i(T), _i(F),
+                                             _stream())
+    else:
+        if block <= 0 or F % block:
+            raise KernelError(f"swiglu: blocks of {block} columns do not divide {F}")
+        st = _lib("elementwise").dlgo_swiglu_blocks(_ptr(gate_up), _ptr(out), _i(dtype_code(gate_up.dtype)), _i(T),
+                                                    _i(F), _i(block), _stream())
     _check(st, "swiglu")
     return out
 
@@ -176,6 +183,8 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.T
 NORM_NONE, NORM_RMS, NORM_DYT = 0, 1, 2
 ACT_NONE, ACT_RELU2, ACT_SILU, ACT_GELU_TANH = 0, 1, 2, 3
 ACT_TANH = 4           # (the elementwise bias_act only)
+MOE_ACT_SWIGLU = 4     # (moe_gemm_tc only: W's rows in blocks of MOE_SWIGLU_BLOCK gate rows and as many up rows)
+MOE_SWIGLU_BLOCK = 16
 GATE_SIGMOID, GATE_SILU = 0, 1
 MAX_STREAMS = 8
 
@@ -939,7 +948,10 @@ def moe_gemm_tc(plan: MoEPlan, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
             out.stride(1) != 1):
         raise KernelError("moe_gemm_tc: a plan with tiles of 128 rows (or 256: CTA pairs), a and out 2-D, w [experts, N, K]")
     E, N, Kd = w.shape
-    if a.shape[1] != Kd or out.shape[1] != N or out.dtype not in (torch.float32, torch.bfloat16):
+    if act == MOE_ACT_SWIGLU and (N % (2 * MOE_SWIGLU_BLOCK) or plan.tile_rows != MOE_TC_ROWS):
+        raise KernelError("moe_gemm_tc: silu(gate) * up needs whole blocks of gate and up rows and tiles of 128 rows")
+    n_out = N // 2 if act == MOE_ACT_SWIGLU else N
+    if a.shape[1] != Kd or out.shape[1] != n_out or out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError("moe_gemm_tc: shapes or types do not fit")
     st = _lib("moe_tc").dlgo_moe_gemm_tc(
         _ptr(a), _ll(a.shape[0]), _ll(a.stride(0)), _ptr(w), _i(E), _ptr(out), _ll(out.stride(0)),

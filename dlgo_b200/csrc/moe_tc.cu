@@ -24,7 +24,10 @@ namespace dlgo {
 using namespace sm100;
 
 constexpr int GT_M = 128, GT_K = 64, GT_UMMA_K = 16, GT_THREADS = 192;
-enum { GT_ACT_NONE = 0, GT_ACT_RELU2 = 1, GT_ACT_SILU = 2, GT_ACT_GELU_TANH = 3 };
+enum { GT_ACT_NONE = 0, GT_ACT_RELU2 = 1, GT_ACT_SILU = 2, GT_ACT_GELU_TANH = 3,
+       // W's rows come in blocks of 16 gate rows followed by their 16 up rows: 32 columns of the accumulator give 16
+       // columns silu(gate) * up of an output that is N / 2 wide (N a multiple of 32; single-CTA tiles only)
+       GT_ACT_SWIGLU16 = 4 };
 
 __device__ int g_moe_tc_error = 0;
 
@@ -179,6 +182,33 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           if (lane == 0) mbar_arrive(&acc_empty[b]);
         }
         if (!mine) continue;
+        if (p.act == GT_ACT_SWIGLU16) {              // (N is a multiple of 32: no ragged edge)
+          const int col = (n0 + c0) >> 1;
+#pragma unroll
+          for (int q = 0; q < 16; ++q) v[q] = v[q] / (1.f + __expf(-v[q])) * v[q + 16];
+          if (p.out_f32) {
+            float* dst = (float*)p.out + dst_row + col;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) dst[q] = v[q];
+          } else {
+            __nv_bfloat16* dst = (__nv_bfloat16*)p.out + dst_row + col;
+            if (((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+              for (int q = 0; q < 16; q += 8) {
+                uint4 o;
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(v[q], v[q + 1]), b1 = __floats2bfloat162_rn(v[q + 2], v[q + 3]);
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(v[q + 4], v[q + 5]), b3 = __floats2bfloat162_rn(v[q + 6], v[q + 7]);
+                o.x = *reinterpret_cast<unsigned*>(&b0); o.y = *reinterpret_cast<unsigned*>(&b1);
+                o.z = *reinterpret_cast<unsigned*>(&b2); o.w = *reinterpret_cast<unsigned*>(&b3);
+                *reinterpret_cast<uint4*>(dst + q) = o;
+              }
+            } else {
+#pragma unroll
+              for (int q = 0; q < 16; ++q) dst[q] = __float2bfloat16_rn(v[q]);
+            }
+          }
+          continue;
+        }
 #pragma unroll
         for (int q = 0; q < 32; ++q) v[q] = gt_act(v[q], p.act);
         const int col = n0 + c0;
@@ -552,6 +582,7 @@ DLGO_EXPORT int dlgo_moe_gemm_tc(const void* A, long long a_rows, long long lda,
                                  int act, int out_f32, cudaStream_t stream) {
   if (max_tiles <= 0 || max_tiles > 65535 || a_rows <= 0 || experts <= 0) return DLGO_ERR_SIZE;
   if (!dlgo_moe_gemm_tc_takes(N, K)) return DLGO_ERR_SIZE;
+  if (act == GT_ACT_SWIGLU16 && (N % 32 != 0 || tile_rows != GT_M)) return DLGO_ERR_SIZE;
   CUtensorMap ma, mb;
   if (tile_rows == 256) {
     // CTA pairs: each CTA fetches its 128 rows and half of a weight tile of 256 columns

@@ -42,6 +42,7 @@ _TENSOR_CORES = os.environ.get("DLGO_MOE_TC", "1") != "0"       # 0: the fp32-pi
 _TC_MIN_PAIRS = int(os.environ.get("DLGO_MOE_TC_MIN_PAIRS", 0))      # 0: 24, or 128 for experts below 2 MB
 # prompts (more than 2,048 pairs): CTA pairs on two row tiles of an expert that share one weight tile
 _TC_PAIRS = os.environ.get("DLGO_MOE_TC_PAIR", "0") != "0"
+_FUSED_SWIGLU = os.environ.get("DLGO_MOE_FUSED_SWIGLU", "1") != "0"     # 0: gated experts' silu(gate) * up as a pass of its own
 
 
 class RoutedExperts(FeedForward):
@@ -126,9 +127,18 @@ class RoutedExperts(FeedForward):
             self.b_logit = get(n["logit_bias"]).to(torch.float32).contiguous()
         if self.num_experts:
             ups = [runtime.compute_copy(get(n["expert"].format(e) + n["up"])) for e in range(self.num_experts)]
-            if self.gated:      # an expert's first matrix: its gate rows, then its up rows
-                ups = [torch.cat([runtime.compute_copy(get(n["expert"].format(e) + n["gate"])), up], dim=0)
-                       for e, up in enumerate(ups)]
+            self.gate_block = self.intermediate_size
+            if self.gated:
+                # an expert's first matrix: its gate rows, then its up rows; in bfloat16, where the tensor-core
+                # contraction forms silu(gate) * up on its accumulator, blocks of 16 gate rows and their 16 up rows
+                f, B = self.intermediate_size, K.MOE_SWIGLU_BLOCK
+                gates = [runtime.compute_copy(get(n["expert"].format(e) + n["gate"])) for e in range(self.num_experts)]
+                if _TENSOR_CORES and _FUSED_SWIGLU and runtime.dtype == torch.bfloat16 and f % B == 0:
+                    self.gate_block = B
+                    ups = [torch.stack([g.view(f // B, B, -1), u.view(f // B, B, -1)], dim=1).reshape(2 * f, -1)
+                           for g, u in zip(gates, ups)]
+                else:
+                    ups = [torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]
             downs = [runtime.compute_copy(get(n["expert"].format(e) + n["down"])) for e in range(self.num_experts)]
             self.w_up = torch.stack(ups, dim=0).contiguous()
             self.w_down = torch.stack(downs, dim=0).contiguous()
@@ -153,21 +163,24 @@ class RoutedExperts(FeedForward):
                                            plan=(self.num_experts, tile_rows), logit_bias=self.b_logit)
         pair_out = None
         if self.num_experts:
-            # (gated: the first contraction leaves gate | up side by side, and silu(gate) * up is a pass of its own)
+            # (gated: the first contraction leaves gate and up values side by side; silu(gate) * up is formed on the
+            # tensor-core kernel's accumulator where the rows alternate in blocks, else by a pass of its own)
             act = K.ACT_NONE if self.gated else self.act
-            hidden = torch.empty((pairs, self.w_up.shape[1]), dtype=x.dtype, device=x.device)
+            fused = self.gated and on_tc and self.gate_block == K.MOE_SWIGLU_BLOCK and tile_rows == K.MOE_TC_ROWS
+            hidden = torch.empty((pairs, self.intermediate_size if fused else self.w_up.shape[1]), dtype=x.dtype,
+                                 device=x.device)
             pair_out = torch.empty((pairs, d), dtype=x.dtype, device=x.device)    # (sums of these stay fp32)
             if on_tc:
                 # bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
                 rows = K.moe_gather_rows(plan, x, self.top)
-                K.moe_gemm_tc(plan, rows, self.w_up, hidden, False, act)
-                if self.gated:
-                    hidden = K.swiglu(hidden)
+                K.moe_gemm_tc(plan, rows, self.w_up, hidden, False, K.MOE_ACT_SWIGLU if fused else act)
+                if self.gated and not fused:
+                    hidden = K.swiglu(hidden, block=self.gate_block)
                 K.moe_gemm_tc(plan, hidden, self.w_down, pair_out, True, K.ACT_NONE)
             else:
                 K.moe_gemm(plan, x, self.w_up, hidden, self.top, False, act)               # rows gathered by token
                 if self.gated:
-                    hidden = K.swiglu(hidden)
+                    hidden = K.swiglu(hidden, block=self.gate_block)
                 K.moe_gemm(plan, hidden, self.w_down, pair_out, None, True, K.ACT_NONE)    # rows scattered by pair
         shared = None
         if self.shared_size is not None:

@@ -260,6 +260,45 @@ def test_experts_on_many_tokens(dtype):
     assert_rows(run_whole(engine_of(cfg, w, dtype), tokens), plain_of(cfg, w, tokens), dtype, "experts, 700 tokens")
 
 
+@pytest.mark.parametrize("T", [5, 300])
+@pytest.mark.parametrize("d, ff, E, top", [(128, 64, 6, 2), (72, 16, 3, 3), (256, 160, 2, 1)])
+def test_gated_experts_on_the_tensor_cores(T, d, ff, E, top):
+    """silu(gate) * up formed on the grouped tensor-core contraction's accumulator (an expert's rows in blocks of
+    16 gate rows and their 16 up rows) and by the pass of its own over both layouts, against fp32 formulas."""
+    from dlgo_b200.csrc import kernels as K
+    g = torch.Generator().manual_seed(T + d + ff)
+    B = K.MOE_SWIGLU_BLOCK
+    h = torch.randn(T, d, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(E, ff, d, generator=g) / d ** 0.5).to(torch.bfloat16)
+    up = (torch.randn(E, ff, d, generator=g) / d ** 0.5).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+    blocks = torch.stack([gate.view(E, ff // B, B, d), up.view(E, ff // B, B, d)], dim=2).reshape(E, 2 * ff, d)
+    ref = torch.zeros(T * top, ff)
+    for t in range(T):
+        for j in range(top):
+            e = int(idx[t, j])
+            a, b = gate[e].float() @ h[t].float(), up[e].float() @ h[t].float()
+            ref[t * top + j] = a * torch.sigmoid(a) * b
+    plan = K.moe_plan(idx.to(DEV), E, K.MOE_TC_ROWS)
+    rows = K.moe_gather_rows(plan, h.to(DEV), top)
+    total = int(plan.offsets[-1])
+    assert total == T * top
+    pair = plan.sorted_pair[:total].long().cpu()
+    hid = torch.full((T * top, ff), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.moe_gemm_tc(plan, rows, blocks.to(DEV), hid, False, K.MOE_ACT_SWIGLU)
+    both = torch.full((T * top, 2 * ff), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.moe_gemm_tc(plan, rows, blocks.to(DEV), both, False, K.ACT_NONE)
+    halves = torch.full((T * top, 2 * ff), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.moe_gemm_tc(plan, rows, torch.cat([gate, up], dim=1).to(DEV), halves, False, K.ACT_NONE)
+    K.check_device_errors()
+    tol = 2e-2 * float(ref.abs().max())
+    for what, got in (("fused", hid), ("pass over blocks", K.swiglu(both, block=B)), ("pass over halves", K.swiglu(halves))):
+        out = torch.zeros(T * top, ff)
+        out[pair] = got[:total].float().cpu()
+        assert torch.isfinite(out).all(), what
+        assert torch.allclose(out, ref, rtol=2e-2, atol=tol), (what, float((out - ref).abs().max()))
+
+
 # ---------------------------------------------- a key that carries the answer: far away, and at the window's edge
 def standing_out(cfg, w):
     """(query token b, key token a, filler f) for a one-layer model whose first mixer is the window attention: a's
