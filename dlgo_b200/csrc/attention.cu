@@ -10,7 +10,8 @@
 // chunk of its query heads), and one slice of the sequence's pages, and runs an
 // online softmax in fp32 over 64-key pages.  With more than one slice the
 // partial (max, sum, unnormalised output) go to scratch and a second kernel
-// combines them.  A window w > 0 keeps keys t > pos - w only.
+// combines them.  A window w > 0 keeps keys t > pos - w only; w < 0 keeps the keys of the query's own chunk of -w
+// positions (first_visible in common.cuh).
 //
 // Storage type T (float or bfloat16) is what q, the pages and the output hold;
 // scores, softmax and the weighted sum are fp32 with expf.
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(AttnParams p) {
   const int slot = p.seq_slot[seq];
   const int pos0 = p.token_pos[tok0];
   const int t_end = pos0 + ntok;  // one past the last key any row may see
-  const int t_begin = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int t_begin = first_visible(pos0, p.window);
   const int pg_first = t_begin / PS, pg_last = (t_end - 1) / PS;
   const int per = (pg_last - pg_first + 1 + p.n_splits - 1) / p.n_splits;
   const int pg_b = pg_first + split * per;
@@ -141,7 +142,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(AttnParams p) {
       const int r = idx / PS, key = idx - r * PS;
       const int t = pg * PS + key;
       const int pos_r = pos0 + r / GC;
-      const bool valid = t <= pos_r && (p.window <= 0 || t > pos_r - p.window);
+      const bool valid = t <= pos_r && t >= first_visible(pos_r, p.window);
       float s = -INFINITY;
       if (valid) {
         const float* qr = q_s + r * hd;

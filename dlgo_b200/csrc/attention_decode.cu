@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 4) attention_decode_kernel(DecPar
   const int slot = p.seq_slot[b];
   const int pos = p.token_pos[b];
   const int t_end = pos + 1;
-  const int t_begin = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int t_begin = first_visible(pos, p.window);     // (a negative window: chunks, see common.cuh)
   const int pg_first = t_begin / PS, pg_last = pos / PS;
   const int per = (pg_last - pg_first + 1 + p.n_splits - 1) / p.n_splits;
   const int pg_b = pg_first + split * per;

@@ -167,7 +167,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int slot = p.seq_slot[seq];
   const int pos0 = p.token_pos[tok0];
   const int t_end = pos0 + ntok;                                  // one past the last key any row sees
-  const int t_begin = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int t_begin = first_visible(pos0, p.window);            // (a negative window: chunks, see common.cuh)
   const int first_live_page = t_begin / 64;                       // pages before it may have been given back
   const int kb_first = t_begin / PF_KEYS, kb_last = (t_end - 1) / PF_KEYS;
   const int nblk = kb_last - kb_first + 1;
@@ -304,9 +304,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
       PF_CLK(1);
-      const int lo = p.window > 0 ? pos_r - p.window : -1;        // keys t > lo and t <= pos_r are seen
+      const int lo = first_visible(pos_r, p.window) - 1;          // keys t > lo and t <= pos_r are seen
       // blocks that lie wholly inside every row's range need no mask (all but the diagonal ones)
-      const bool full_block = (k0 + PF_KEYS - 1 <= pos0) && (p.window <= 0 || k0 > pos0 + ntok - 1 - p.window);
+      const bool full_block = (k0 + PF_KEYS - 1 <= pos0) && k0 >= first_visible(pos0 + ntok - 1, p.window);
       if (!full_block) {
 #pragma unroll
         for (int j = 0; j < PF_KEYS; ++j) {

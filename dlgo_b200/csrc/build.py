@@ -49,6 +49,8 @@ LIBRARIES: Dict[str, List[str]] = {
     "layernorm": ["layernorm.cu"],
     "timemix": ["timemix.cu"],
     "wholenorm_append": ["wholenorm_append.cu"],
+    "conv_rope_append": ["conv_rope_append.cu"],
+    "gated_residual": ["gated_residual.cu"],
 }
 _HEADERS = ["common.cuh", "attention_noalloc.h", "attention_combine.cuh", "attention_decode_tiles.cuh", "tcgen05.cuh",
             "async_copy.cuh"]

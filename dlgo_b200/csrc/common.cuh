@@ -170,6 +170,16 @@ __device__ unsigned long long g_times[1024 * 8];
 #define DLGO_TIMES_EXPORT
 #endif
 
+// Which keys t <= pos a query at position pos sees, as ONE integer `span` that every attention kernel takes where
+// it takes a window: span > 0 is a sliding window (keys t > pos - span), span < 0 cuts the sequence into chunks of
+// -span positions counted from position 0 (keys of the query's own chunk only), 0 is every key.  The first visible
+// key; it never decreases as pos grows.
+__host__ __device__ __forceinline__ int first_visible(int pos, int span) {
+  if (span > 0) return pos - span + 1 > 0 ? pos - span + 1 : 0;
+  if (span < 0) return pos - pos % (-span);
+  return 0;
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? DLGO_OK : (int)e;

@@ -14,7 +14,7 @@ namespace dlgo {
 // ---------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                             float* __restrict__ out, int d, int vocab, int copies) {
+                             float* __restrict__ out, int d, int vocab, int copies, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -25,7 +25,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
   if (copies > 1) {
     // several residual streams: every copy starts as the embedding
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-      const float v = ok ? to_float(row[i]) : 0.f;
+      const float v = ok ? to_float(row[i]) * scale : 0.f;
       for (int c = 0; c < copies; ++c) o[(size_t)c * d + i] = v;
     }
     return;
@@ -37,12 +37,12 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
       const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
       const float2 c = __bfloat1622float2(h[2]), e = __bfloat1622float2(h[3]);
-      *reinterpret_cast<float4*>(o + i) = make_float4(a.x, a.y, b.x, b.y);
-      *reinterpret_cast<float4*>(o + i + 4) = make_float4(c.x, c.y, e.x, e.y);
+      *reinterpret_cast<float4*>(o + i) = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+      *reinterpret_cast<float4*>(o + i + 4) = make_float4(c.x * scale, c.y * scale, e.x * scale, e.y * scale);
     }
     return;
   }
-  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_float(row[i]) * scale : 0.f;
 }
 
 // ------------------------------------------------------------------ RMSNorm
@@ -318,16 +318,16 @@ __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, int
 
 using namespace dlgo;
 
-// tokens[T] int32, table[vocab, d] (f32 or bf16), out[T, d] f32
+// tokens[T] int32, table[vocab, d] (f32 or bf16), out[T, d] f32; every number times `scale` (fp32)
 DLGO_EXPORT int dlgo_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int d,
-                           int vocab, int copies, cudaStream_t stream) {
+                           int vocab, int copies, float scale, cudaStream_t stream) {
   if (T <= 0) return DLGO_OK;
   if (d <= 0 || vocab <= 0 || copies < 1) return DLGO_ERR_SIZE;
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == DLGO_F32)
-    launch_kernel_first(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab, copies);
+    launch_kernel_first(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab, copies, scale);
   else if (table_dtype == DLGO_BF16)
-    launch_kernel_first(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, d, vocab, copies);
+    launch_kernel_first(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, tokens, (const __nv_bfloat16*)table, out, d, vocab, copies, scale);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();

@@ -102,8 +102,8 @@ _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlo
 
 # ------------------------------------------------------------------ elementwise
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None,
-          copies: Optional[int] = None) -> torch.Tensor:
-    """out[t, :] = table[tokens[t], :] as fp32; with ``copies`` = s, out[t, c, :] for c < s (all equal)."""
+          copies: Optional[int] = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t, :] = table[tokens[t], :] * scale as fp32; with ``copies`` = s, out[t, c, :] for c < s (all equal)."""
     _need(tokens, torch.int32, "tokens")
     _need(table, None, "table")
     T, (V, d) = tokens.numel(), table.shape
@@ -111,7 +111,7 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor]
         out = torch.empty((T, d) if copies is None else (T, copies, d), dtype=torch.float32, device=table.device)
     _need(out, torch.float32, "out")
     st = _lib("elementwise").dlgo_embed(_ptr(tokens), _ptr(table), _i(dtype_code(table.dtype)), _ptr(out), _i(T), _i(d),
-                                        _i(V), _i(copies or 1), _stream())
+                                        _i(V), _i(copies or 1), _f(scale), _stream())
     _check(st, "embed")
     return out
 
@@ -312,6 +312,34 @@ def latent_norm_append(proj: torch.Tensor, kv_off: int, kv_rank: int, w_kv: torc
         _ptr(pages), _i(dtype_code(pages.dtype)), _i(pages.shape[-2]), _i(1 if write_cache else 0), _stream())
     _check(st, "latent_norm_append")
     return cq
+
+
+def latent_rope_append(proj: torch.Tensor, kv_off: int, kv_rank: int, w_kv: torch.Tensor, q_off: int, num_heads: int,
+                       q_head: int, rope: int, freq: torch.Tensor, amplitude: float, eps: float,
+                       token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
+                       page_table: torch.Tensor, pages: torch.Tensor, write_cache: bool = True) -> None:
+    """Latents with a rotated key part, from fp32 ``proj`` [T, ld]: columns ``kv_off ...`` hold ``kv_rank`` numbers
+    that are RMS-normed (times ``w_kv``) and ``rope`` numbers that turn with the position in neighbouring pairs
+    (angle ``float(pos) * freq[i]``, cosine and sine times ``amplitude``); both go to the token's row of the paged
+    cache ``pages`` [n, 1, page, kv_rank + rope].  The queries at ``q_off`` ([heads, q_head] per token) turn IN
+    PLACE in the last ``rope`` numbers of every head."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("latent_rope_append: proj must be 2-D float32 with unit inner stride")
+    _need(w_kv, torch.float32, "w_kv")
+    _need(freq, torch.float32, "freq")
+    _need(pages, None, "pages")
+    for n, t in (("token_pos", token_pos), ("token_seq", token_seq), ("seq_slot", seq_slot), ("page_table", page_table)):
+        _need(t, torch.int32, n)
+    if pages.shape[-1] != kv_rank + rope or w_kv.numel() != kv_rank or freq.numel() != rope // 2:
+        raise KernelError("latent_rope_append: cache rows hold kv_rank + rope numbers; rope / 2 frequencies")
+    if q_off + num_heads * q_head > proj.shape[1] or kv_off + kv_rank + rope > proj.shape[1]:
+        raise KernelError("latent_rope_append: the columns named lie outside proj")
+    st = _lib("latent_attention").dlgo_latent_rope_append(
+        _ptr(proj), _i(proj.stride(0)), _i(proj.shape[0]), _i(kv_off), _i(kv_rank), _ptr(w_kv), _i(q_off),
+        _i(num_heads), _i(q_head), _i(rope), _ptr(freq), _f(amplitude), _f(eps), _ptr(token_pos), _ptr(token_seq),
+        _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]), _ptr(pages), _i(dtype_code(pages.dtype)),
+        _i(pages.shape[-2]), _i(1 if write_cache else 0), _stream())
+    _check(st, "latent_rope_append")
 
 
 def latent_attention(q: torch.Tensor, w_k: torch.Tensor, w_v: torch.Tensor, sink: Optional[torch.Tensor],
@@ -672,6 +700,111 @@ def wholenorm_append(proj: torch.Tensor, w_q: Optional[torch.Tensor], w_k: Optio
     return q, gate
 
 
+CONV_MAX_TAPS = 8
+
+
+def conv_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], taps: Optional[torch.Tensor],
+                     state: Optional[torch.Tensor], freq: Optional[torch.Tensor], rot: int, amplitude: float,
+                     token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
+                     page_table: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, num_heads: int,
+                     num_kv_heads: int, qk_dim: int, v_dim: int, tiles: Optional[torch.Tensor], n_tiles: int,
+                     write_cache: bool = True) -> torch.Tensor:
+    """From the fp32 result ``proj`` [T, >= C] of a q | k | v projection (heads of ``qk_dim``, ``qk_dim`` and ``v_dim``
+    numbers, C in all): ``+ bias`` [C]; a causal convolution over time per channel with ``taps`` [C, n] (the last
+    tap on the token itself), whose reach before the step's first token of a sequence is read from ``state``
+    [slots, n - 1, C] (fp32; afterwards it holds the sequence's last n - 1 projected rows: a second launch over
+    ``tiles`` [n_tiles, 3], one row (sequence, first packed token, count) per sequence of the step); rotation of
+    the first ``rot`` numbers of every q and k head in neighbouring pairs (angle ``float(pos) * freq[i]``, cosine and
+    sine times ``amplitude``); k and v into their page rows, q returned [T, heads * hd] in the cache's type, heads
+    laid out ``hd`` = the pages' head size wide with zeros behind their own numbers."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("conv_rope_append: proj must be 2-D float32 with unit inner stride")
+    C = (num_heads + num_kv_heads) * qk_dim + num_kv_heads * v_dim
+    hd = kpages.shape[-1]
+    if proj.shape[1] < C or kpages.shape != vpages.shape or kpages.dtype != vpages.dtype:
+        raise KernelError("conv_rope_append: proj has too few columns, or keys and values differ in shape")
+    n_taps = 1
+    for n, t, numel in (("bias", bias, C), ("freq", freq, rot // 2)):
+        if t is not None:
+            _need(t, torch.float32, n)
+            if t.numel() != numel:
+                raise KernelError(f"conv_rope_append: {n} has {t.numel()} numbers, wanted {numel}")
+    if taps is not None:
+        _need(taps, torch.float32, "taps")
+        if taps.dim() != 2 or taps.shape[0] != C or not 1 <= taps.shape[1] <= CONV_MAX_TAPS:
+            raise KernelError(f"conv_rope_append: taps must be [channels, 1..{CONV_MAX_TAPS}]")
+        n_taps = taps.shape[1]
+    if n_taps > 1:
+        if state is None or tiles is None:
+            raise KernelError("conv_rope_append: a convolution needs the sequences' state and the step's sequences")
+        _need(state, torch.float32, "state")
+        _need(tiles, torch.int32, "tiles")
+        if state[0].numel() != (n_taps - 1) * C:
+            raise KernelError("conv_rope_append: a state row holds (taps - 1) * channels numbers")
+    for n, t in (("token_pos", token_pos), ("token_seq", token_seq), ("seq_slot", seq_slot), ("page_table", page_table)):
+        _need(t, torch.int32, n)
+    _need(kpages, None, "kpages")
+    _need(vpages, None, "vpages")
+    T = proj.shape[0]
+    q = torch.empty((T, num_heads * hd), dtype=kpages.dtype, device=proj.device)
+    st = _lib("conv_rope_append").dlgo_conv_rope_append(
+        _ptr(proj), _i(proj.stride(0)), _i(T), _ptr(bias), _ptr(taps), _i(n_taps), _ptr(state), _ptr(freq), _i(rot),
+        _f(amplitude), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]),
+        _i(kpages.shape[-2]), _ptr(q), _ptr(kpages), _ptr(vpages), _i(dtype_code(kpages.dtype)), _i(num_heads),
+        _i(num_kv_heads), _i(qk_dim), _i(v_dim), _i(hd), _i(1 if write_cache else 0), _ptr(tiles), _i(n_tiles),
+        _stream())
+    _check(st, "conv_rope_append", 2 if n_taps > 1 else 1)
+    return q
+
+
+def gated_residual(x: torch.Tensor, y: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                   gate_bias: Optional[torch.Tensor], *, history: Optional[torch.Tensor] = None, depth: int = 0,
+                   average: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                   out_dtype: Optional[torch.dtype] = None, clear_y: bool = True) -> Optional[torch.Tensor]:
+    """``x += y * sigmoid(gate + gate_bias)`` on the fp32 stream ``x`` [T, d] (``gate`` None: ``x += y``; ``y`` None:
+    nothing is added), ``y`` left zero; with ``depth`` = n > 0, x is then stored as entry n - 1 of ``history``
+    [>= n, T, d] and replaced by ``sum_j average[j] * history[j]`` over j < n; with ``norm_w``, the RMS norm of the
+    new x times ``norm_w`` comes back in ``out_dtype``."""
+    _need(x, torch.float32, "x")
+    T, d = x.shape
+    if y is not None:
+        _need(y, torch.float32, "y")
+        if tuple(y.shape) != (T, d):
+            raise KernelError("gated_residual: y must have x's shape")
+    ldg = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < d:
+            raise KernelError("gated_residual: gate must be fp32 [T, >= d] with unit inner stride")
+        ldg = gate.stride(0)
+    if gate_bias is not None:
+        _need(gate_bias, torch.float32, "gate_bias")
+    stride = 0
+    if depth > 0:
+        _need(history, torch.float32, "history")
+        _need(average, torch.float32, "average")
+        if history.dim() != 3 or history.shape[0] < depth or tuple(history.shape[1:]) != (T, d) or average.numel() != depth:
+            raise KernelError("gated_residual: history must be [>= depth, T, d] and average hold depth numbers")
+        stride = history.stride(0)
+    out = None
+    if norm_w is not None:
+        _need(norm_w, torch.float32, "norm_w")
+        out = torch.empty((T, d), dtype=out_dtype, device=x.device)
+    st = _lib("gated_residual").dlgo_gated_residual(
+        _ptr(x), _ptr(y), _ptr(gate), _i(ldg), _ptr(gate_bias), _ptr(history), _ll(stride), _i(depth), _ptr(average),
+        _ptr(norm_w), _f(eps), _ptr(out), _i(dtype_code(out_dtype) if out is not None else F32), _i(T), _i(d),
+        _i(1 if clear_y else 0), _stream())
+    _check(st, "gated_residual")
+    return out
+
+
+def scale_softcap(logits: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+    """``logits <- cap * tanh(logits * scale / cap)`` in place on contiguous fp32 (``cap`` <= 0: ``logits * scale``)."""
+    _need(logits, torch.float32, "logits")
+    st = _lib("gated_residual").dlgo_scale_softcap(_ptr(logits), _ll(logits.numel()), _f(scale), _f(cap), _stream())
+    _check(st, "scale_softcap")
+    return logits
+
+
 def scale_heads(a: torch.Tensor, gate: torch.Tensor, head_dim: int) -> torch.Tensor:
     """``a[t, h, :] *= gate[t, h]`` in place for ``a`` [T, H * head_dim] (float32 or bfloat16) and fp32 ``gate`` [T, H]."""
     _need(a, None, "a")
@@ -960,6 +1093,22 @@ def moe_gemm_tc(plan: MoEPlan, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
         _i(1 if out.dtype == torch.float32 else 0), _stream())
     _check(st, "moe_gemm_tc")
     return out
+
+
+def moe_scale_rows(h: torch.Tensor, wt: torch.Tensor) -> tuple:
+    """For experts whose weight multiplies their input: (rows [T * top, d] with ``rows[t * top + k] = wt[t, k] *
+    h[t]`` in ``h``'s type, ones [T, top] fp32 as the weights the combine then uses)."""
+    _need(wt, torch.float32, "wt")
+    if h.dim() != 2 or h.stride(1) != 1 or wt.dim() != 2 or wt.shape[0] != h.shape[0]:
+        raise KernelError("moe_scale_rows: h [T, d] with unit inner stride, wt [T, top]")
+    T, d = h.shape
+    top = wt.shape[1]
+    rows = torch.empty((T * top, d), dtype=h.dtype, device=h.device)
+    ones = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    st = _lib("moe").dlgo_moe_scale_rows(_ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(wt), _ptr(rows),
+                                         _ptr(ones), _i(T * top), _i(d), _i(top), _stream())
+    _check(st, "moe_scale_rows")
+    return rows, ones
 
 
 def moe_combine(y: torch.Tensor, pair_out: Optional[torch.Tensor], h: torch.Tensor, idx: torch.Tensor,

@@ -52,6 +52,68 @@ __global__ void latent_norm_append_kernel(const float* __restrict__ proj, int ld
   for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = from_float<T>(x[i] * sc * w[i]);
 }
 
+// The same for latents that carry a rotated key part: the down-projection has kv_rank + rope numbers; the first
+// kv_rank are normed (times w_kv) as above, the last `rope` are one key part shared by all heads, which turns with
+// the position (entries 2i and 2i + 1 by the angle pos * freq[i], cosine and sine times `amplitude`) and is kept
+// behind the latent in the same cache row ([.., page, kv_rank + rope]).  Queries q [T, H, dq] (fp32, inside
+// proj at q_off) turn in place in their last `rope` numbers of every head.  blockIdx.y: 0 the cache row, 1 the
+// queries.  Angles are float(pos) * freq in fp32.
+template <typename T>
+__global__ void latent_rope_append_kernel(float* proj, int ld, int kv_off, int kv_rank, const float* __restrict__ w_kv,
+                                          int q_off, int H, int dq, int rope, const float* __restrict__ freq,
+                                          float amplitude, float eps, const int* __restrict__ token_pos,
+                                          const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                          const int* __restrict__ page_table, int max_pages, T* pages, int page_size,
+                                          int write_cache) {
+  pdl_launch_dependents();
+  __shared__ float scratch[32];
+  __shared__ float scale_s;
+  const int t = blockIdx.x;
+  const int pos = token_pos[t];
+  const int half = rope / 2;
+  if (blockIdx.y == 1) {
+    pdl_wait();
+    float* q = proj + (size_t)t * ld + q_off;
+    for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+      const int h = idx / half, i = idx - h * half;
+      float* pair = q + (size_t)h * dq + (dq - rope) + 2 * i;
+      float sn, cs;
+      sincosf((float)pos * freq[i], &sn, &cs);
+      sn *= amplitude;
+      cs *= amplitude;
+      const float u = pair[0], v = pair[1];
+      pair[0] = u * cs - v * sn;
+      pair[1] = v * cs + u * sn;
+    }
+    return;
+  }
+  T* dst = nullptr;
+  if (write_cache) {
+    const int slot = seq_slot[token_seq[t]];
+    const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+    if (page >= 0) dst = pages + ((size_t)page * page_size + pos % page_size) * (kv_rank + rope);
+  }
+  pdl_wait();
+  if (dst == nullptr) return;
+  const float* x = proj + (size_t)t * ld + kv_off;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0) scale_s = 1.0f / sqrtf(ss / (float)kv_rank + eps);
+  __syncthreads();
+  const float sc = scale_s;
+  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) dst[i] = from_float<T>(x[i] * sc * w_kv[i]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    sincosf((float)pos * freq[i], &sn, &cs);
+    sn *= amplitude;
+    cs *= amplitude;
+    const float u = x[kv_rank + 2 * i], v = x[kv_rank + 2 * i + 1];
+    dst[kv_rank + 2 * i] = from_float<T>(u * cs - v * sn);
+    dst[kv_rank + 2 * i + 1] = from_float<T>(v * cs + u * sn);
+  }
+}
+
 // Latents of the pages a prompt step attends, gathered into rows [n_tmp * page_size, rank] (row = temporary page
 // * page_size + place in the page) for the contraction that makes the step's keys and values.  `tmp_pages`
 // [n_tmp, 3]: (sequence of the step, its page index, rows of the page that are written); other rows are zero.
@@ -562,6 +624,29 @@ DLGO_EXPORT int dlgo_latent_norm_append(const float* proj, int ld, int T_tokens,
     launch_kernel(latent_norm_append_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, proj, ld, kv_off, kv_rank,
                   w_kv, q_off, q_rank, w_q, (__nv_bfloat16*)cq, eps, token_pos, token_seq, seq_slot, page_table,
                   max_pages, (__nv_bfloat16*)pages, page_size, write_cache);
+  else
+    return DLGO_ERR_DTYPE;
+  return launch_status();
+}
+
+DLGO_EXPORT int dlgo_latent_rope_append(float* proj, int ld, int T_tokens, int kv_off, int kv_rank, const float* w_kv,
+                                        int q_off, int H, int dq, int rope, const float* freq, float amplitude,
+                                        float eps, const int* token_pos, const int* token_seq, const int* seq_slot,
+                                        const int* page_table, int max_pages, void* pages, int dtype, int page_size,
+                                        int write_cache, cudaStream_t stream) {
+  if (T_tokens <= 0) return DLGO_OK;
+  if (kv_rank <= 0 || page_size <= 0 || rope <= 0 || (rope & 1) || rope > dq || H <= 0 || freq == nullptr)
+    return DLGO_ERR_SIZE;
+  const dim3 grid(T_tokens, 2);
+  const int threads = kv_rank >= 1024 ? 256 : 128;
+  if (dtype == DLGO_F32)
+    launch_kernel(latent_rope_append_kernel<float>, grid, dim3(threads), 0, stream, proj, ld, kv_off, kv_rank, w_kv,
+                  q_off, H, dq, rope, freq, amplitude, eps, token_pos, token_seq, seq_slot, page_table, max_pages,
+                  (float*)pages, page_size, write_cache);
+  else if (dtype == DLGO_BF16)
+    launch_kernel(latent_rope_append_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, proj, ld, kv_off, kv_rank,
+                  w_kv, q_off, H, dq, rope, freq, amplitude, eps, token_pos, token_seq, seq_slot, page_table, max_pages,
+                  (__nv_bfloat16*)pages, page_size, write_cache);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();

@@ -20,7 +20,7 @@ from typing import Any, Callable, Dict, Mapping, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import CacheNeed, Mixer, ParamSpec, PositionEncoding
+from .base import CacheNeed, Mixer, ParamSpec, PositionEncoding, StateNeed
 from .linear import ADD_F32, STORE, STORE_F32, Linear, stack_rows
 from .registry import MIXERS
 
@@ -67,6 +67,7 @@ class GQAAttention(Mixer):
         self.window = None if window is None else int(window)
         self.position_encoding = position_encoding
         self.cache_group = cache_group
+        self.chunk: Optional[int] = None      # a subclass may cut the sequence into chunks instead of a window
         self.q_dim = self.num_heads * self.head_dim
         self.kv_dim = self.num_kv_heads * self.head_dim
         self.wqkv: Optional[Linear] = None
@@ -92,6 +93,13 @@ class GQAAttention(Mixer):
         self.wqkv = Linear(torch.cat(parts, dim=0), runtime)
         self.wo = Linear(get("o_proj.weight"), runtime)
         self._no_rotation = torch.zeros((1, 1), dtype=torch.float32, device=runtime.device)
+
+    def span(self) -> int:
+        """Which keys a query sees besides the causal rule, as the attention kernels take it: a window w as w, chunks
+        of c positions as -c, every key as 0."""
+        if self.window:
+            return self.window
+        return -self.chunk if self.chunk else 0
 
     # -------------------------------------------------------------------- forward
     def _decode_slices(self, ctx: Any, cache: Any, T: int, group: int, pages: int):
@@ -146,17 +154,17 @@ class GQAAttention(Mixer):
         if mma:
             K.attention_decode_mma(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
                                    ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                                   self.window or 0, n_splits, _MMA_KEYS, scratch)
+                                   self.span(), n_splits, _MMA_KEYS, scratch)
         elif decode_kernel:
             K.attention_decode(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
                                ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim, self.scale,
-                               self.window or 0, n_splits, scratch, counters)
+                               self.span(), n_splits, scratch, counters)
         elif not ctx.decode and K.attention_prefill_tc_takes(qkv.dtype, self.head_dim, cache.page_size):
             # prompts: 128 query rows per CTA on the tensor cores
             tiles, n_tiles, _ = ctx.tiles(K.PREFILL_TC_TILE, heaviest_first=True)
             K.attention_prefill_tc(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles,
                                    ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads,
-                                   self.head_dim, self.scale, self.window or 0)
+                                   self.head_dim, self.scale, self.span())
         else:
             qt, gchunk = K.attention_tile_shape(self.head_dim, group, ctx.decode)
             tiles, n_tiles, tile_max = ctx.tiles(qt)
@@ -170,7 +178,7 @@ class GQAAttention(Mixer):
                                       K.attention_scratch_floats(T, self.num_heads, self.head_dim, n_splits))
             K.attention(qkv, qkv.stride(0), T, cache.keys, cache.values, cache.page_table, tiles, tile_max,
                         ctx.seq_slot, ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim,
-                        self.scale, self.window or 0, n_splits, gchunk, scratch)
+                        self.scale, self.span(), n_splits, gchunk, scratch)
 
     def _project_out(self, out: torch.Tensor, residual: torch.Tensor, ctx: Any) -> None:
         parts = self.wo.partials(out, for_residual=True) if hasattr(ctx, "defer") else None
@@ -209,7 +217,7 @@ class GQAAttention(Mixer):
                 # the decode kernel rotates, appends and clears itself: no launch for the rotation
                 K.attention_decode_mma(None, n_cols, T, cache.keys, cache.values, cache.page_table, ctx.seq_slot,
                                        ctx.token_pos, out, self.num_heads, self.num_kv_heads, self.head_dim,
-                                       self.scale, self.window or 0, n_splits, _MMA_KEYS, None, qkv_sum, cos, sin,
+                                       self.scale, self.span(), n_splits, _MMA_KEYS, None, qkv_sum, cos, sin,
                                        cache.writes, clear_parts=True)
                 rotated = True
             else:
@@ -317,6 +325,8 @@ class KeysAsValuesAttention(GQAAttention):
         freq, rot = None, 0
         if self.position_encoding is not None:
             pe = positions[self.position_encoding]
+            if getattr(pe, "interleaved", False) or getattr(pe, "amplitude", 1.0) != 1.0:
+                raise ValueError("this mixer's kernel rotates pairs (i, i + rot/2) with plain cosine and sine")
             freq, rot = pe.frequencies, pe.rotary_dim
         act = self.wqk.weight.dtype
         n_cols = self.q_dim + self.kv_dim
@@ -436,6 +446,129 @@ class WholeNormAttention(GQAAttention):
         self._project_out(out, residual, ctx)
 
 
+_WHOLE_SEQUENCE = 1 << 30
+
+
+class ShortConvAttention(GQAAttention):
+    """Grouped-query softmax attention whose projections carry biases and pass through a short causal convolution
+    over time before the rotation, whose keys and values may differ in size, and whose mask may be cut into chunks:
+
+        q = Wq h + bq,  k = Wk h + bk,  v = Wv h + bv                 (``bias``; H x qk_dim, G x qk_dim, G x v_dim)
+        u_t <- sum_j taps[c, j] * u_(t - n + 1 + j)  per channel c    (``conv_taps`` n > 1; zeros before the sequence)
+        q, k: the rotation named by ``position_encoding`` (neighbouring pairs of the first numbers of each head)
+        out_h = softmax over the visible keys of (q_h . k_g * scale) v_g     g = h // (H / G)
+        visible: j <= i and, with ``window`` w, i - j < w; or, with ``chunk`` c, floor(i / c) = floor(j / c)
+        result = Wo [out_1 .. out_H] + bo
+
+    The sequence's last n - 1 projected rows (with their biases, fp32) are its state.  Heads are laid out
+    ``head_dim`` = max(qk_dim, v_dim) (rounded up to a multiple of 8) numbers wide with zeros behind their own
+    numbers, so that keys and values share the page shape and the kernels of :class:`GQAAttention` run unchanged.
+    The projection's result stays fp32 until bias, convolution and rotation are done (one kernel, which also
+    appends to the cache; a second small one keeps the state).  A chunked mixer keeps all its pages: the cache
+    manager's window bookkeeping is for sliding windows.  ``names``: tensor names below the part's prefix."""
+
+    head_multiple = 8
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, qk_dim: int, v_dim: int, scale: float,
+                 bias: bool = False, conv_taps: Optional[int] = None, window: Optional[int] = None,
+                 chunk: Optional[int] = None, position_encoding: Optional[str] = None, cache_group: str = "full",
+                 names: Optional[Mapping[str, str]] = None):
+        self.qk_dim, self.v_dim = int(qk_dim), int(v_dim)
+        if self.qk_dim <= 0 or self.v_dim <= 0:
+            raise ValueError("qk_dim and v_dim must be positive")
+        if window is not None and chunk is not None:
+            raise ValueError("a window or chunks, not both")
+        if chunk is not None and chunk <= 0:
+            raise ValueError(f"chunk must be positive or None, got {chunk}")
+        taps = int(conv_taps or 1)
+        if not 1 <= taps <= K.CONV_MAX_TAPS:
+            raise ValueError(f"conv_taps must be 1 to {K.CONV_MAX_TAPS}, got {conv_taps}")
+        padded = -(-max(self.qk_dim, self.v_dim) // self.head_multiple) * self.head_multiple
+        super().__init__(hidden_size, num_heads, num_kv_heads, padded, scale, window, position_encoding, cache_group)
+        self.params = dict(hidden_size=hidden_size, num_heads=num_heads, num_kv_heads=num_kv_heads, qk_dim=qk_dim,
+                           v_dim=v_dim, scale=scale, bias=bias, conv_taps=conv_taps, window=window, chunk=chunk,
+                           position_encoding=position_encoding, cache_group=cache_group, names=names)
+        self.chunk = None if chunk is None else int(chunk)
+        self.bias = bool(bias)
+        self.taps = taps
+        self.channels = (self.num_heads + self.num_kv_heads) * self.qk_dim + self.num_kv_heads * self.v_dim
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "out": "o_proj.weight",
+                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+                      "out_bias": "o_proj.bias", "q_conv": "q_conv.weight", "k_conv": "k_conv.weight",
+                      "v_conv": "v_conv.weight"}
+        self.names.update(names or {})
+        self.w_in: Optional[Linear] = None        # rows q | k | v
+        self.b_in: Optional[torch.Tensor] = None
+        self.b_out: Optional[torch.Tensor] = None
+        self.w_taps: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n, d = self.names, self.hidden_size
+        H, G, dk, dv = self.num_heads, self.num_kv_heads, self.qk_dim, self.v_dim
+        sizes = {"q": H * dk, "k": G * dk, "v": G * dv}
+        specs = {n[key]: ParamSpec((rows, d)) for key, rows in sizes.items()}
+        specs[n["out"]] = ParamSpec((d, H * dv))
+        if self.bias:
+            for key, rows in sizes.items():
+                specs[n[key + "_bias"]] = ParamSpec((rows,))
+            specs[n["out_bias"]] = ParamSpec((d,))
+        if self.taps > 1:
+            for key, rows in sizes.items():
+                specs[n[key + "_conv"]] = ParamSpec((rows, self.taps), "last_one_plus_normal")
+        return specs
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(self.cache_group, self.num_kv_heads, self.head_dim, self.window)
+
+    def state_need(self) -> Optional[StateNeed]:
+        return StateNeed(((self.taps - 1) * self.channels,), torch.float32) if self.taps > 1 else None
+
+    def load(self, get: Callable[[str], torch.Tensor], runtime: Any) -> None:
+        n = self.names
+        self.w_in = Linear(stack_rows([runtime.compute_copy(get(n[key])) for key in ("q", "k", "v")]), runtime)
+        wo = runtime.compute_copy(get(n["out"]))
+        hd, dv, H = self.head_dim, self.v_dim, self.num_heads
+        if dv != hd:        # zero columns where the heads' layout has zeros
+            wide = torch.zeros((wo.shape[0], H, hd), dtype=wo.dtype, device=wo.device)
+            wide[:, :, :dv] = wo.view(wo.shape[0], H, dv)
+            wo = wide.view(wo.shape[0], H * hd)
+        self.wo = Linear(wo.contiguous(), runtime)
+        if self.bias:       # added in fp32: to the projection's fp32 result, and to the fp32 sum the mixer adds into
+            self.b_in = torch.cat([get(n[key + "_bias"]).to(torch.float32) for key in ("q", "k", "v")]).contiguous()
+            self.b_out = get(n["out_bias"]).to(torch.float32).contiguous()
+        if self.taps > 1:
+            self.w_taps = torch.cat([get(n[key + "_conv"]).to(torch.float32) for key in ("q", "k", "v")],
+                                    dim=0).contiguous()
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
+                state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
+        T = ctx.n_tokens
+        act = self.w_in.weight.dtype
+        freq, rot, amplitude = None, 0, 1.0
+        if self.position_encoding is not None:
+            pe = positions[self.position_encoding]
+            if not pe.interleaved:
+                raise ValueError("this mixer's kernel rotates neighbouring pairs: the encoding must be 'interleaved'")
+            freq, rot, amplitude = pe.frequencies, pe.rotary_dim, pe.amplitude
+        tiles, n_tiles = None, 0
+        if self.taps > 1:
+            if state is None:
+                raise RuntimeError("a mixer with a convolution over time needs its state")
+            state = state.view(state.shape[0], -1)
+            tiles, n_tiles, _ = ctx.tiles(1 if ctx.decode else _WHOLE_SEQUENCE)
+        decode_kernel, mma, n_splits, scratch, counters, pages = self._decode_plan(ctx, cache, act)
+        proj = self.w_in(x, STORE_F32)
+        q = K.conv_rope_append(proj, self.b_in, self.w_taps, state, freq, rot, amplitude, ctx.token_pos, ctx.token_seq,
+                               ctx.seq_slot, cache.page_table, cache.keys, cache.values, self.num_heads,
+                               self.num_kv_heads, self.qk_dim, self.v_dim, tiles, n_tiles, cache.writes)
+        out = torch.empty((T, self.q_dim), dtype=act, device=x.device)
+        self._attend(q, ctx, cache, out, decode_kernel, mma, n_splits, scratch, counters, pages)
+        if self.b_out is not None:
+            K.bias_act(residual, self.b_out, K.ACT_NONE, torch.float32, in_place=True)
+        self.wo(out, ADD_F32, residual)
+
+
 MIXERS.register("gqa_attention", GQAAttention)
+MIXERS.register("short_conv_attention", ShortConvAttention)
 MIXERS.register("wholenorm_attention", WholeNormAttention)
 MIXERS.register("keys_as_values_attention", KeysAsValuesAttention)

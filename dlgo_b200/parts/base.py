@@ -33,7 +33,10 @@ class ParamSpec:
 
     ``init`` says how the random-weights mode fills it: ``"normal"`` is
     N(0, std), ``"one_plus_normal"`` is 1 + N(0, std) (norm weights),
-    ``"identity_plus_normal"`` is I + N(0, std) for a square matrix.
+    ``"identity_plus_normal"`` is I + N(0, std) for a square matrix,
+    ``"last_one_plus_normal"`` adds 1 to the last entry along the last axis
+    (taps of a convolution over time, weights of an average whose last term
+    is the newest: the part starts out near the identity).
     """
 
     shape: Tuple[int, ...]

@@ -246,9 +246,123 @@ class ResultNormBlock(Block):
         ctx.residual_copy = (residual, x)
 
 
+class ResidualGate(Part):
+    """A gate on a sublayer's result before it joins the residual stream: ``sigmoid(W h + b)`` element by element,
+    with h the sublayer's own input; W is [size, size].  ``names``: tensor names of W and b below the part's
+    prefix."""
+
+    def __init__(self, size: int, names: Optional[Mapping[str, str]] = None):
+        super().__init__(size=size, names=names)
+        self.size = int(size)
+        self.names = {"weight": "weight", "bias": "bias"}
+        self.names.update(names or {})
+        self.proj: Any = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def param_specs(self):
+        return {self.names["weight"]: ParamSpec((self.size, self.size)), self.names["bias"]: ParamSpec((self.size,))}
+
+    def load(self, get: Any, runtime: Any) -> None:
+        from .linear import Linear
+        self.proj = Linear(get(self.names["weight"]), runtime)
+        self.bias = get(self.names["bias"]).to(torch.float32).contiguous()      # added to the fp32 logits
+
+    def logits(self, h: torch.Tensor) -> torch.Tensor:
+        """``W h`` as fp32 [T, size]; bias and sigmoid belong to the pass that applies the gate."""
+        return self.proj(h, K.EPI_STORE_F32)
+
+
+class DepthAverage(Part):
+    """What a layer hands on is a weighted sum over the depth of the model: with X_0 the embedding's output and X_j
+    the result of the layer j - 1 before this averaging, the layer with ``depth`` = n hands on
+    ``sum_(j < n) a[j] X_j`` (so the first layer has n = 2).  ``total``: the largest ``depth`` in the model (the step
+    keeps that many copies of the stream).  ``name``: the tensor's name below the part's prefix."""
+
+    def __init__(self, depth: int, total: int, name: str = "weight"):
+        super().__init__(depth=depth, total=total, name=name)
+        if not 2 <= int(depth) <= int(total):
+            raise ValueError(f"depth must be 2 to total ({total}), got {depth}")
+        self.depth, self.total = int(depth), int(total)
+        self.name = name
+        self.weights: Optional[torch.Tensor] = None
+
+    def param_specs(self):
+        return {self.name: ParamSpec((self.depth,), "last_one_plus_normal")}
+
+    def load(self, get: Any, runtime: Any) -> None:
+        self.weights = get(self.name).to(torch.float32).contiguous()       # part of the residual sum: fp32
+        self.one = torch.ones((1,), dtype=torch.float32, device=self.weights.device)
+
+
+class GatedPreNormBlock(Block):
+    """Pre-norm layer whose sublayers return through a gate, optionally followed by an average over the depth:
+
+        x <- x + sigmoid(G1 n1 + b1) * mixer(n1),   n1 = norm1(x)
+        x <- x + sigmoid(G2 n2 + b2) * ffn(n2),     n2 = norm2(x)          (a layer without feed-forward ends above)
+        x <- sum_j a[j] X_j                                                (``depth_average``; X_j: see DepthAverage)
+
+    Connections: ``mixer_gate`` and ``ffn_gate`` (:class:`ResidualGate`; a sublayer without one is added as it is),
+    ``depth_average`` (:class:`DepthAverage`).  The residual stream stays fp32; a sublayer adds its result into a
+    zeroed fp32 [tokens, hidden] buffer as it would into a residual stream, and ONE launch applies the gate, adds,
+    leaves the buffer zero, forms the depth average where the layer ends, and norms what the next sublayer reads."""
+
+    handles_pending = False
+
+    def __init__(self, mixer: Any, ffn: Any, norms: Mapping[str, Any], connections: Any = None):
+        super().__init__(mixer, ffn, norms, connections)
+        if mixer is None:
+            raise ValueError("a block needs a mixer")
+        self.sublayers = []
+        for part, norm, gate in ((mixer, "mixer_norm", "mixer_gate"), (ffn, "ffn_norm", "ffn_gate")):
+            if part is None:
+                continue
+            n = self.norms.get(norm)
+            if n is None or not (hasattr(n, "weight") and hasattr(n, "eps")) or getattr(n, "normed_kind", None) != K.NORMED_RMS:
+                raise ValueError(f"a gated pre-norm block needs an RMS norm as {norm!r}")
+            g = self.connections.get(gate)
+            if g is not None and not hasattr(g, "logits"):
+                raise ValueError(f"the connection {gate!r} must be a residual gate")
+            self.sublayers.append((part, n, g))
+        self.average = self.connections.get("depth_average")
+        if self.average is not None and not hasattr(self.average, "depth"):
+            raise ValueError("the connection 'depth_average' must be a depth average")
+
+    def forward(self, residual: torch.Tensor, ctx: Any, cache: Any, state: Optional[torch.Tensor],
+                positions: Mapping[str, PositionEncoding]) -> None:
+        T, d = residual.shape
+        dtype = ctx.runtime.dtype
+        y = ctx.zeros(f"sublayer_out{d}", T * d, torch.float32)[:T * d].view(T, d)
+        avg, history = self.average, None
+        if avg is not None:
+            history = ctx.scratch("depth_history", avg.total * T * d)[:avg.total * T * d].view(avg.total, T, d)
+            if avg.depth == 2:      # the model's first layer: what arrives is the embedding's output X_0
+                K.gated_residual(residual, None, None, None, history=history, depth=1, average=avg.one)
+        first_norm = self.sublayers[0][1]
+        x = first_norm.forward(residual)
+        last = len(self.sublayers) - 1
+        for i, (part, norm, gate) in enumerate(self.sublayers):
+            if part is self.mixer:
+                part.forward(x, y, ctx, cache, state, positions)
+            else:
+                part.forward(x, y, ctx)
+            ctx.settle(y)
+            logits = gate.logits(x) if gate is not None else None
+            bias = gate.bias if gate is not None else None
+            if i < last:
+                nxt = self.sublayers[i + 1][1]
+                x = K.gated_residual(residual, y, logits, bias, norm_w=nxt.weight, eps=nxt.eps, out_dtype=dtype)
+            elif avg is not None:
+                K.gated_residual(residual, y, logits, bias, history=history, depth=avg.depth, average=avg.weights)
+            else:
+                K.gated_residual(residual, y, logits, bias)
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("gated_prenorm", GatedPreNormBlock)
 BLOCKS.register("result_norm", ResultNormBlock)
 BLOCKS.register("hyper_prenorm", HyperPreNormBlock)
 BLOCKS.register("postnorm", PostNormBlock)
 CONNECTIONS.register("hyper_connection", HyperConnection)
 CONNECTIONS.register("layer_scale", LayerScale)
+CONNECTIONS.register("residual_gate", ResidualGate)
+CONNECTIONS.register("depth_average", DepthAverage)

@@ -20,10 +20,13 @@ from .registry import EMBEDDINGS, HEADS
 class TokenEmbedding(Part):
     """``name``: the table's tensor name below the part's prefix.  ``norm``: a norm applied to the looked-up rows
     before they become the residual stream, as ``(kind, params)`` of the norm registry (its tensor names are
-    relative to the embedding's prefix as well); it must offer ``forward_in_place`` on fp32 rows."""
+    relative to the embedding's prefix as well); it must offer ``forward_in_place`` on fp32 rows.  ``scale``: a constant
+    every looked-up number is multiplied by (in fp32)."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, name: str = "weight", norm: Optional[Sequence[Any]] = None):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, name=name, norm=norm)
+    def __init__(self, vocab_size: int, hidden_size: int, name: str = "weight", norm: Optional[Sequence[Any]] = None,
+                 scale: float = 1.0):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, name=name, norm=norm, scale=scale)
+        self.scale = float(scale)
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
         self.name = name
@@ -51,17 +54,24 @@ class TokenEmbedding(Part):
     def forward(self, token_ids: torch.Tensor, copies: Optional[int] = None) -> torch.Tensor:
         """fp32 rows [T, hidden]; with ``copies`` = s, [T, s, hidden] with every copy equal (residual streams)."""
         if self.norm is None:
-            return K.embed(token_ids, self.table, copies=copies)
+            return K.embed(token_ids, self.table, copies=copies, scale=self.scale)
         if copies is not None:
             raise ValueError("a normed embedding feeds a single residual stream")
-        return self.norm.forward_in_place(K.embed(token_ids, self.table))
+        return self.norm.forward_in_place(K.embed(token_ids, self.table, scale=self.scale))
 
 
 class LinearHead(Part):
-    """``tied_to`` names the tensor (absolute name) the head shares, or ``None`` for a weight of its own."""
+    """``tied_to`` names the tensor (absolute name) the head shares, or ``None`` for a weight of its own.
+    ``scale`` s and ``softcap`` c: ``logits <- c * tanh(s * logits / c)`` (c None: ``s * logits``), in fp32."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None, name: str = "weight"):
-        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied_to=tied_to, name=name)
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None, name: str = "weight",
+                 scale: float = 1.0, softcap: Optional[float] = None):
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, tied_to=tied_to, name=name, scale=scale,
+                         softcap=softcap)
+        if softcap is not None and softcap <= 0:
+            raise ValueError(f"softcap must be positive or None, got {softcap}")
+        self.scale = float(scale)
+        self.softcap = None if softcap is None else float(softcap)
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
         self.tied_to = tied_to
@@ -75,7 +85,10 @@ class LinearHead(Part):
         self.proj = Linear(get(self.name), runtime)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.proj(x, STORE_F32)
+        logits = self.proj(x, STORE_F32)
+        if self.scale != 1.0 or self.softcap is not None:
+            K.scale_softcap(logits, self.scale, self.softcap or 0.0)
+        return logits
 
 
 EMBEDDINGS.register("token_embedding", TokenEmbedding)

@@ -11,6 +11,8 @@
                   (``gated``: Wdown_e (silu(Wgate_e h) * (Wup_e h)), a third matrix per expert)
     expert_e(h) = h                                           for the ``identity_experts`` outputs after them
     y += gate * shared(h),  gate = sigmoid(w_g . h) per token (``shared_size``, ``shared_gate``)
+    ``weight_on`` = "input": y = sum over the chosen e of expert_e(s_e * h) instead (the weight multiplies what the
+    expert reads, which differs from the above as soon as an expert is not linear)
 
 Every constant above is a parameter.  Nothing returns to the host between the router and the result: the
 (token, choice) pairs are sorted by expert on the device, the experts run as two grouped contractions over the
@@ -50,12 +52,18 @@ class RoutedExperts(FeedForward):
                  identity_experts: int = 0, group_count: int = 1, group_keep: int = 1, score: str = "softmax",
                  renormalize: bool = False, correction: bool = False, activation: str = "relu2",
                  shared_size: Optional[int] = None, shared_gate: bool = False,
-                 names: Optional[Mapping[str, str]] = None, logit_bias: bool = False, gated: bool = False):
+                 names: Optional[Mapping[str, str]] = None, logit_bias: bool = False, gated: bool = False,
+                 weight_on: str = "output"):
         super().__init__(hidden_size=hidden_size, intermediate_size=intermediate_size, num_experts=num_experts, top=top,
                          identity_experts=identity_experts, group_count=group_count, group_keep=group_keep,
                          score=score, renormalize=renormalize, correction=correction, activation=activation,
                          shared_size=shared_size, shared_gate=shared_gate, names=names, logit_bias=logit_bias,
-                         gated=gated)
+                         gated=gated, weight_on=weight_on)
+        if weight_on not in ("output", "input"):
+            raise ValueError(f"weight_on must be 'output' or 'input', got {weight_on!r}")
+        if weight_on == "input" and identity_experts:
+            raise ValueError("identity experts take their weight on the output")
+        self.weight_on_input = weight_on == "input"
         self.logit_bias = bool(logit_bias)
         self.gated = bool(gated)
         if self.gated and activation != "silu":
@@ -162,6 +170,11 @@ class RoutedExperts(FeedForward):
                                            self.group_count, self.group_keep, self.sigmoid_scores, self.renormalize,
                                            plan=(self.num_experts, tile_rows), logit_bias=self.b_logit)
         pair_out = None
+        src, div = x, self.top
+        if self.weight_on_input:
+            # a row per pair, already multiplied by its weight; the combine then adds the experts' results as they are
+            src, wt = K.moe_scale_rows(x, wt)
+            div = 1
         if self.num_experts:
             # (gated: the first contraction leaves gate and up values side by side; silu(gate) * up is formed on the
             # tensor-core kernel's accumulator where the rows alternate in blocks, else by a pass of its own)
@@ -172,13 +185,13 @@ class RoutedExperts(FeedForward):
             pair_out = torch.empty((pairs, d), dtype=x.dtype, device=x.device)    # (sums of these stay fp32)
             if on_tc:
                 # bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
-                rows = K.moe_gather_rows(plan, x, self.top)
+                rows = K.moe_gather_rows(plan, src, div)
                 K.moe_gemm_tc(plan, rows, self.w_up, hidden, False, K.MOE_ACT_SWIGLU if fused else act)
                 if self.gated and not fused:
                     hidden = K.swiglu(hidden, block=self.gate_block)
                 K.moe_gemm_tc(plan, hidden, self.w_down, pair_out, True, K.ACT_NONE)
             else:
-                K.moe_gemm(plan, x, self.w_up, hidden, self.top, False, act)               # rows gathered by token
+                K.moe_gemm(plan, src, self.w_up, hidden, div, False, act)                  # rows gathered by token (or pair)
                 if self.gated:
                     hidden = K.swiglu(hidden, block=self.gate_block)
                 K.moe_gemm(plan, hidden, self.w_down, pair_out, None, True, K.ACT_NONE)    # rows scattered by pair

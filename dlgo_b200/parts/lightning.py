@@ -138,6 +138,8 @@ class Retention(Mixer):
         freq, rot = None, 0
         if self.position_encoding is not None:
             pe = positions[self.position_encoding]
+            if getattr(pe, "interleaved", False) or getattr(pe, "amplitude", 1.0) != 1.0:
+                raise ValueError("this mixer's kernel rotates pairs (i, i + rot/2) with plain cosine and sine")
             freq, rot = pe.frequencies, pe.rotary_dim
         if rot or self.k_scale != 1.0:
             K.rotate_scale(proj, 0, H * dk, freq, rot, ctx.token_pos, H, dk, self.k_scale)

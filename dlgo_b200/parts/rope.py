@@ -12,6 +12,13 @@ scaling at all); it follows the published Llama 3.1 rule: with wavelength
 ``lam = 2*pi/f``, frequencies with ``lam < orig/high`` are kept, those with
 ``lam > orig/low`` are divided by ``factor``, and those between are blended by
 ``s = (orig/lam - low) / (high - low)``: ``f <- (1-s) * f/factor + s * f``.
+
+YaRN scaling (``rope_type`` "yarn": ``factor``, ``original_max_position_embeddings``, ``beta_fast``,
+``beta_slow``) blends by the pair's index instead.  With ``where(t) = rot * ln(orig / (2 pi t)) / (2 ln base)`` (the
+index whose pair makes t turns over the original context), ``lo = max(floor(where(beta_fast)), 0)``,
+``hi = min(ceil(where(beta_slow)), rot - 1)`` and ``r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``:
+``f_i <- r_i * f_i / factor + (1 - r_i) * f_i``; cosine and sine are multiplied by ``0.1 ln(factor) + 1``
+(:func:`rotary_amplitude`).
 """
 from __future__ import annotations
 
@@ -30,6 +37,19 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: Optional[Dict[str
     if not scaling:
         return freqs
     kind = scaling.get("rope_type", "llama3")
+    if kind == "yarn":
+        factor = float(scaling["factor"])
+        orig = float(scaling["original_max_position_embeddings"])
+
+        def where(turns: float) -> float:
+            return rotary_dim * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+        lo = max(math.floor(where(float(scaling["beta_fast"]))), 0)
+        hi = min(math.ceil(where(float(scaling["beta_slow"]))), rotary_dim - 1)
+        out = []
+        for i, f in enumerate(freqs):
+            r = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / factor * r + f * (1.0 - r))
+        return out
     if kind != "llama3":
         raise ValueError(f"rotary scaling {kind!r} is not supported")
     factor = float(scaling["factor"])
@@ -47,6 +67,13 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: Optional[Dict[str
             s = (orig / lam - low) / (high - low)
             out.append((1.0 - s) * f / factor + s * f)
     return out
+
+
+def rotary_amplitude(scaling: Optional[Dict[str, Any]]) -> float:
+    """The factor on cosine and sine that a scaling rule brings with it (YaRN: ``0.1 ln(factor) + 1``; else 1)."""
+    if scaling and scaling.get("rope_type") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 class RotaryEmbedding(PositionEncoding):
@@ -72,7 +99,8 @@ class RotaryEmbedding(PositionEncoding):
         f = torch.tensor(rotary_frequencies(self.rotary_dim, self.theta, self.scaling), dtype=torch.float64)
         pos = torch.arange(self.max_positions, dtype=torch.float64)
         ang = pos[:, None] * f[None, :]
-        return torch.cos(ang).to(torch.float32), torch.sin(ang).to(torch.float32)
+        a = rotary_amplitude(self.scaling)
+        return (torch.cos(ang) * a).to(torch.float32), (torch.sin(ang) * a).to(torch.float32)
 
     def prepare(self, runtime: Any) -> None:
         c, s = self.tables()
@@ -83,17 +111,23 @@ class RotaryEmbedding(PositionEncoding):
 class RotaryFrequencies(PositionEncoding):
     """Rotary positions without tables: only the frequencies ``f_i = theta^(-2i/rotary_dim)`` (float64, rounded
     to float32) are kept; a kernel that rotates forms the angle ``float(position) * f_i`` in fp32 and takes its
-    cosine and sine itself, so no context limit is built in.  Pairs are (i, i + rotary_dim/2)."""
+    cosine and sine itself, so no context limit is built in.  ``pairing``: ``split_half`` pairs (i, i + rotary_dim/2),
+    ``interleaved`` pairs (2i, 2i + 1); a kernel takes the one it is written for.  :attr:`amplitude` is the factor
+    on cosine and sine that the scaling rule brings (1 without one)."""
 
-    def __init__(self, head_dim: int, rotary_dim: int, theta: float, scaling: Optional[Dict[str, Any]] = None):
-        super().__init__(head_dim=head_dim, rotary_dim=rotary_dim, theta=theta, scaling=scaling)
+    def __init__(self, head_dim: int, rotary_dim: int, theta: float, scaling: Optional[Dict[str, Any]] = None,
+                 pairing: str = "split_half"):
+        super().__init__(head_dim=head_dim, rotary_dim=rotary_dim, theta=theta, scaling=scaling, pairing=pairing)
+        if pairing not in ("split_half", "interleaved"):
+            raise ValueError(f"pairing must be 'split_half' or 'interleaved', got {pairing!r}")
         if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
             raise ValueError(f"rotary_dim must be even and in (0, head_dim], got {rotary_dim} for head_dim {head_dim}")
         self.head_dim = int(head_dim)
         self.rotary_dim = int(rotary_dim)
         self.theta = float(theta)
-        self.interleaved = False
+        self.interleaved = pairing == "interleaved"
         self.scaling = dict(scaling) if scaling else None
+        self.amplitude = rotary_amplitude(self.scaling)
         self.frequencies: Optional[torch.Tensor] = None
 
     def prepare(self, runtime: Any) -> None:

@@ -43,6 +43,8 @@ def write_random_model(config: Any, seed: int, out_dir: str, std: float = 0.02,
             t = t + 1.0
         elif spec.init == "identity_plus_normal":
             t = t + torch.eye(spec.shape[0], device=dev)
+        elif spec.init == "last_one_plus_normal":
+            t[..., -1] += 1.0
         elif spec.init != "normal":
             raise ValueError(f"tensor {name!r}: unknown init {spec.init!r}")
         return t.to(dtype)
