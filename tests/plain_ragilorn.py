@@ -195,3 +195,10 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, layers_out: Optional[
     z = rms_norm(x, w["final.norm"], eps) @ w["head"].T * cfg["logit_scale"]
     cap = cfg.get("logit_softcap")
     return cap * torch.tanh(z / cap) if cap else z
+
+
+def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt, n: int) -> List[int]:
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(forward(cfg, w, tokens)[-1].argmax()))
+    return tokens[len(prompt):]
