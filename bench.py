@@ -423,6 +423,43 @@ def bazurax_pair(size):
     return baz, llama
 
 
+# --only ragilorn: the Ragilorn design beside Llama at equal layer sizes (random weights)
+RAGILORN_SIZES = {
+    # width, heads / kv heads, head size and rotated numbers of the attention layers, their chunk; heads, unrotated and
+    # rotated query sizes, value size and latent size of the latent-attention layers; dense feed-forward; experts
+    "small": dict(width=1024, heads=16, kv=4, dim=64, rot=32, chunk=512, lheads=16, ldim=32, lrot=32, lv=64, rank=256,
+                  ff=2816, experts=16, top=2, eff=1408, vocab=32000),
+    "1b": dict(width=2048, heads=16, kv=4, dim=128, rot=64, chunk=1024, lheads=16, ldim=64, lrot=64, lv=128, rank=512,
+               ff=5632, experts=32, top=4, eff=1408, vocab=32000),
+    "3b": dict(width=3072, heads=24, kv=8, dim=128, rot=64, chunk=1024, lheads=24, ldim=64, lrot=64, lv=128, rank=512,
+               ff=8192, experts=32, top=4, eff=2048, vocab=32000),
+}
+
+
+def ragilorn_pair(size):
+    """(Ragilorn config.json, Llama config.json): four layers, one of each pairing of mixer (chunked attention with
+    a convolution over time; latent attention with a rotated key part) and feed-forward (dense; experts whose chosen
+    ones spend the dense one's FLOPs), every sublayer behind its gate, a depth average after every layer; Llama
+    with as many layers of the same width, heads, head size and dense feed-forward."""
+    z = RAGILORN_SIZES[size]
+    scaling = {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "conv": 4, "mask": {"size": z["chunk"]}, "rot": {"base": 500000.0, "dims": z["rot"], "scaling": scaling}}
+    lat = {"heads": z["lheads"], "dim": z["ldim"], "rot_dim": z["lrot"], "vdim": z["lv"], "kv_rank": z["rank"],
+           "scale": (z["ldim"] + z["lrot"]) ** -0.5, "rot": {"base": 1e6, "dims": z["lrot"], "scaling": scaling}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    rag = {"architecture": "Ragilorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+           "embedding": {"scale": 1.0}, "logit_scale": 1.0, "logit_softcap": 30.0,
+           "layers": [{"type": "attention", "mixer": att, "mlp": dense}, {"type": "latent_attention", "mixer": lat, "mlp": moe},
+                      {"type": "attention", "mixer": att, "mlp": moe}, {"type": "latent_attention", "mixer": lat, "mlp": dense}]}
+    llama = dict(architectures=["LlamaForCausalLM"], hidden_size=z["width"], num_hidden_layers=4,
+                 intermediate_size=z["ff"], num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["dim"],
+                 vocab_size=z["vocab"], rope_theta=500000.0, rope_scaling=None, rms_norm_eps=1e-5,
+                 max_position_embeddings=8192, tie_word_embeddings=False)
+    return rag, llama
+
+
 def dedutar_compare(size, batch, steps, warmup, prefill_tokens, profile, design="dedutar"):
     """Prefill and decode throughput of both models, and (with `profile`) the time per kernel entry point of
     one prompt step and of decode steps launched one by one."""
@@ -433,7 +470,7 @@ def dedutar_compare(size, batch, steps, warmup, prefill_tokens, profile, design=
     from dlgo_b200.weights import write_random_model
     out = {"only": design, "size": size, "batch": batch, "prefill_tokens": prefill_tokens, "dtype": "bf16",
            "data": "synthetic", "models": {}}
-    pair = {"monolix": monolix_pair, "dedutar": dedutar_pair, "bazurax": bazurax_pair}[design](size)
+    pair = {"monolix": monolix_pair, "dedutar": dedutar_pair, "bazurax": bazurax_pair, "ragilorn": ragilorn_pair}[design](size)
     for name, cfg in zip((design, "llama"), pair):
         tmp = tempfile.mkdtemp(prefix=f"bench_{name}_")
         try:
@@ -530,10 +567,11 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="--only prefill: tokens of the prompt")
     ap.add_argument("--prefill-batch", type=int, default=0,
                     help="--only prefill: a packed batch of that many prompts with lengths from --prompt-range")
-    ap.add_argument("--only", choices=["decode", "prefill", "phases", "sampled", "dedutar", "monolix", "bazurax"],
+    ap.add_argument("--only", choices=["decode", "prefill", "phases", "sampled", "dedutar", "monolix", "bazurax", "ragilorn"],
                     help="run one small workload (for profiling) and stop; phases: see phase_stamps(); dedutar, "
-                         "monolix, bazurax: prefill and decode of that design beside Llama at equal layer sizes")
+                         "monolix, bazurax, ragilorn: prefill and decode of that design beside Llama at equal layer sizes")
     ap.add_argument("--bazurax-size", default="1b", choices=sorted(BAZURAX_SIZES), help="--only bazurax: layer sizes")
+    ap.add_argument("--ragilorn-size", default="1b", choices=sorted(RAGILORN_SIZES), help="--only ragilorn: layer sizes")
     ap.add_argument("--monolix-size", default="1b", choices=sorted(MONOLIX_SIZES), help="--only monolix: layer sizes")
     ap.add_argument("--dedutar-size", default="1b", choices=sorted(DEDUTAR_SIZES), help="--only dedutar: layer sizes")
     ap.add_argument("--kernels", action="store_true", help="--only dedutar / monolix / bazurax: also the time per kernel entry point")
@@ -559,6 +597,10 @@ def main() -> int:
     if a.only == "monolix":
         print(json.dumps(dedutar_compare(a.monolix_size, a.batch, a.steps, warmup, a.prefill_tokens, a.kernels,
                                          design="monolix")))
+        return 0
+    if a.only == "ragilorn":
+        print(json.dumps(dedutar_compare(a.ragilorn_size, a.batch, a.steps, warmup, a.prefill_tokens, a.kernels,
+                                         design="ragilorn")))
         return 0
     if a.only == "bazurax":
         print(json.dumps(dedutar_compare(a.bazurax_size, a.batch, a.steps, warmup, a.prefill_tokens, a.kernels,

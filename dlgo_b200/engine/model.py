@@ -40,6 +40,10 @@ class CausalLM:
                 raise ValueError(f"layer {len(self.blocks) - 1}: the block {ls.block!r} does not fit a model "
                                  f"{'with' if spec.streams is not None else 'without'} residual streams")
         self.order = list(spec.order)
+        # a block may do its successor's first step in its own last launch (a norm of the stream it has just written)
+        for a, b in zip(self.order, self.order[1:]):
+            if hasattr(self.blocks[a.layer], "link_next"):
+                self.blocks[a.layer].link_next(self.blocks[b.layer])
         for i, e in enumerate(self.order):
             if e.cache_of is not None:
                 mine = self._cache_need(e.layer)

@@ -86,6 +86,7 @@ class StepContext:
     owed: Optional[dict] = None              # a write into several residual streams that the next reader performs
     residual_copy: Optional[tuple] = None    # (residual stream, its current rows in the run's type), kept by blocks that make one
     sublayer_input_f32: Optional[torch.Tensor] = None   # the fp32 stream a sublayer reads, where its block offers it
+    normed_ahead: Optional[tuple] = None     # (residual stream, norm, its rows normed by that norm): made by a block's last launch for its successor
     _tiles: Dict[Tuple[int, bool], Tuple[torch.Tensor, int, int]] = field(default_factory=dict)
     _scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
 

@@ -304,7 +304,8 @@ class GatedPreNormBlock(Block):
     Connections: ``mixer_gate`` and ``ffn_gate`` (:class:`ResidualGate`; a sublayer without one is added as it is),
     ``depth_average`` (:class:`DepthAverage`).  The residual stream stays fp32; a sublayer adds its result into a
     zeroed fp32 [tokens, hidden] buffer as it would into a residual stream, and ONE launch applies the gate, adds,
-    leaves the buffer zero, forms the depth average where the layer ends, and norms what the next sublayer reads."""
+    leaves the buffer zero, forms the depth average where the layer ends, and norms what the next sublayer reads
+    (across layers too: a layer whose successor in the run order is of this kind norms for it, ``link_next``)."""
 
     handles_pending = False
 
@@ -326,6 +327,16 @@ class GatedPreNormBlock(Block):
         self.average = self.connections.get("depth_average")
         if self.average is not None and not hasattr(self.average, "depth"):
             raise ValueError("the connection 'depth_average' must be a depth average")
+        self._next_norm: Any = None
+        self._next_known = False
+
+    def link_next(self, nxt: Any) -> None:
+        """Told by the model which block follows this one in the run order: if it is always the same block of this
+        kind, this block's last launch also norms the stream with that block's first norm."""
+        norm = nxt.sublayers[0][1] if isinstance(nxt, GatedPreNormBlock) else None
+        if self._next_known and norm is not self._next_norm:
+            norm = None             # (a layer that runs in several places with different successors)
+        self._next_norm, self._next_known = norm, True
 
     def forward(self, residual: torch.Tensor, ctx: Any, cache: Any, state: Optional[torch.Tensor],
                 positions: Mapping[str, PositionEncoding]) -> None:
@@ -338,8 +349,12 @@ class GatedPreNormBlock(Block):
             if avg.depth == 2:      # the model's first layer: what arrives is the embedding's output X_0
                 K.gated_residual(residual, None, None, None, history=history, depth=1, average=avg.one)
         first_norm = self.sublayers[0][1]
-        x = first_norm.forward(residual)
+        ahead, ctx.normed_ahead = getattr(ctx, "normed_ahead", None), None
+        x = ahead[2] if ahead is not None and ahead[0] is residual and ahead[1] is first_norm else \
+            first_norm.forward(residual)
         last = len(self.sublayers) - 1
+        nn = self._next_norm
+        tail = dict(norm_w=nn.weight, eps=nn.eps, out_dtype=dtype) if nn is not None else {}
         for i, (part, norm, gate) in enumerate(self.sublayers):
             if part is self.mixer:
                 part.forward(x, y, ctx, cache, state, positions)
@@ -352,9 +367,12 @@ class GatedPreNormBlock(Block):
                 nxt = self.sublayers[i + 1][1]
                 x = K.gated_residual(residual, y, logits, bias, norm_w=nxt.weight, eps=nxt.eps, out_dtype=dtype)
             elif avg is not None:
-                K.gated_residual(residual, y, logits, bias, history=history, depth=avg.depth, average=avg.weights)
+                x = K.gated_residual(residual, y, logits, bias, history=history, depth=avg.depth, average=avg.weights,
+                                     **tail)
             else:
-                K.gated_residual(residual, y, logits, bias)
+                x = K.gated_residual(residual, y, logits, bias, **tail)
+        if nn is not None:
+            ctx.normed_ahead = (residual, nn, x)
 
 
 BLOCKS.register("prenorm", PreNormBlock)
