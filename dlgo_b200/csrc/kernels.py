@@ -708,15 +708,17 @@ def conv_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], taps: Opt
                      token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
                      page_table: torch.Tensor, kpages: torch.Tensor, vpages: torch.Tensor, num_heads: int,
                      num_kv_heads: int, qk_dim: int, v_dim: int, tiles: Optional[torch.Tensor], n_tiles: int,
-                     write_cache: bool = True) -> torch.Tensor:
+                     write_cache: bool = True, one_token_each: bool = False, clear_proj: bool = False) -> torch.Tensor:
     """From the fp32 result ``proj`` [T, >= C] of a q | k | v projection (heads of ``qk_dim``, ``qk_dim`` and ``v_dim``
     numbers, C in all): ``+ bias`` [C]; a causal convolution over time per channel with ``taps`` [C, n] (the last
     tap on the token itself), whose reach before the step's first token of a sequence is read from ``state``
     [slots, n - 1, C] (fp32; afterwards it holds the sequence's last n - 1 projected rows: a second launch over
-    ``tiles`` [n_tiles, 3], one row (sequence, first packed token, count) per sequence of the step); rotation of
-    the first ``rot`` numbers of every q and k head in neighbouring pairs (angle ``float(pos) * freq[i]``, cosine and
-    sine times ``amplitude``); k and v into their page rows, q returned [T, heads * hd] in the cache's type, heads
-    laid out ``hd`` = the pages' head size wide with zeros behind their own numbers."""
+    ``tiles`` [n_tiles, 3], one row (sequence, first packed token, count) per sequence of the step, which a step
+    whose sequences bring one token each, ``one_token_each``, may do without; such a step may also hand ``proj`` as
+    a sum to be left zero, ``clear_proj``, where :func:`conv_rope_append_clears` says so); rotation of the first ``rot`` numbers
+    of every q and k head in neighbouring pairs (angle ``float(pos) * freq[i]``, cosine and sine times
+    ``amplitude``); k and v into their page rows, q returned [T, heads * hd] in the cache's type, heads laid out
+    ``hd`` = the pages' head size wide with zeros behind their own numbers."""
     if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1:
         raise KernelError("conv_rope_append: proj must be 2-D float32 with unit inner stride")
     C = (num_heads + num_kv_heads) * qk_dim + num_kv_heads * v_dim
@@ -752,17 +754,24 @@ def conv_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], taps: Opt
         _f(amplitude), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), _i(page_table.shape[1]),
         _i(kpages.shape[-2]), _ptr(q), _ptr(kpages), _ptr(vpages), _i(dtype_code(kpages.dtype)), _i(num_heads),
         _i(num_kv_heads), _i(qk_dim), _i(v_dim), _i(hd), _i(1 if write_cache else 0), _ptr(tiles), _i(n_tiles),
-        _stream())
+        _i(1 if one_token_each else 0), _i(1 if clear_proj else 0), _stream())
     _check(st, "conv_rope_append", 2 if n_taps > 1 else 1)
     return q
 
 
+def conv_rope_append_clears(qk_dim: int, v_dim: int, head_dim: int, ld: int, n_taps: int) -> bool:
+    """Whether :func:`conv_rope_append` can clear ``proj`` (row stride ``ld``) behind it in a step of one token a sequence."""
+    return bool(_lib("conv_rope_append").dlgo_conv_rope_append_clears(_i(qk_dim), _i(v_dim), _i(head_dim), _i(ld), _i(n_taps)))
+
+
 def gated_residual(x: torch.Tensor, y: Optional[torch.Tensor], gate: Optional[torch.Tensor],
-                   gate_bias: Optional[torch.Tensor], *, history: Optional[torch.Tensor] = None, depth: int = 0,
+                   gate_bias: Optional[torch.Tensor], *, y_bias: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None, depth: int = 0,
                    average: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
-                   out_dtype: Optional[torch.dtype] = None, clear_y: bool = True) -> Optional[torch.Tensor]:
-    """``x += y * sigmoid(gate + gate_bias)`` on the fp32 stream ``x`` [T, d] (``gate`` None: ``x += y``; ``y`` None:
-    nothing is added), ``y`` left zero; with ``depth`` = n > 0, x is then stored as entry n - 1 of ``history``
+                   out_dtype: Optional[torch.dtype] = None, clear_y: bool = True,
+                   clear_gate: bool = False) -> Optional[torch.Tensor]:
+    """``x += (y + y_bias) * sigmoid(gate + gate_bias)`` on the fp32 stream ``x`` [T, d] (``gate`` None: ``x += y +
+    y_bias``; ``y`` None: nothing is added; ``y_bias`` [d]: a bias the sublayer left to this pass), ``y`` left zero
+    (and ``gate`` with ``clear_gate``: a sum that a contraction's slices add themselves into); with ``depth`` = n > 0, x is then stored as entry n - 1 of ``history``
     [>= n, T, d] and replaced by ``sum_j average[j] * history[j]`` over j < n; with ``norm_w``, the RMS norm of the
     new x times ``norm_w`` comes back in ``out_dtype``."""
     _need(x, torch.float32, "x")
@@ -776,8 +785,11 @@ def gated_residual(x: torch.Tensor, y: Optional[torch.Tensor], gate: Optional[to
         if gate.dtype != torch.float32 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < d:
             raise KernelError("gated_residual: gate must be fp32 [T, >= d] with unit inner stride")
         ldg = gate.stride(0)
-    if gate_bias is not None:
-        _need(gate_bias, torch.float32, "gate_bias")
+    for n, t in (("gate_bias", gate_bias), ("y_bias", y_bias)):
+        if t is not None:
+            _need(t, torch.float32, n)
+            if t.numel() != d:
+                raise KernelError(f"gated_residual: {n} must hold {d} numbers")
     stride = 0
     if depth > 0:
         _need(history, torch.float32, "history")
@@ -790,9 +802,9 @@ def gated_residual(x: torch.Tensor, y: Optional[torch.Tensor], gate: Optional[to
         _need(norm_w, torch.float32, "norm_w")
         out = torch.empty((T, d), dtype=out_dtype, device=x.device)
     st = _lib("gated_residual").dlgo_gated_residual(
-        _ptr(x), _ptr(y), _ptr(gate), _i(ldg), _ptr(gate_bias), _ptr(history), _ll(stride), _i(depth), _ptr(average),
+        _ptr(x), _ptr(y), _ptr(y_bias), _ptr(gate), _i(ldg), _ptr(gate_bias), _ptr(history), _ll(stride), _i(depth), _ptr(average),
         _ptr(norm_w), _f(eps), _ptr(out), _i(dtype_code(out_dtype) if out is not None else F32), _i(T), _i(d),
-        _i(1 if clear_y else 0), _stream())
+        _i(1 if clear_y else 0), _i(1 if clear_gate else 0), _stream())
     _check(st, "gated_residual")
     return out
 
@@ -1055,9 +1067,14 @@ def moe_gemm_tc_takes(dtype: torch.dtype, n: int, k: int) -> bool:
     return dtype == torch.bfloat16 and n > 0 and k > 0 and k % 8 == 0
 
 
-def moe_gather_rows(plan: MoEPlan, src: torch.Tensor, div: int) -> torch.Tensor:
+def moe_gather_rows(plan: MoEPlan, src: torch.Tensor, div: int, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows of ``src`` in the plan's sorted order: ``dst[r] = src[pair(r) // div]`` for the rows that belong to
-    an expert (the others are left unwritten).  Rows must be a multiple of 16 bytes."""
+    an expert (the others are left unwritten).  Rows must be a multiple of 16 bytes.  ``scale`` (fp32, one number
+    per pair; bfloat16 rows only): ``dst[r] = scale[pair(r)] * src[pair(r) // div]``."""
+    if scale is not None:
+        _need(scale, torch.float32, "scale")
+        if src.dtype != torch.bfloat16 or scale.numel() != plan.pairs:
+            raise KernelError("moe_gather_rows: a scale goes with bfloat16 rows, one number per pair")
     if src.dim() != 2 or src.stride(1) != 1:
         raise KernelError("moe_gather_rows: src must be 2-D with unit inner stride")
     if not src.is_cuda:
@@ -1066,7 +1083,7 @@ def moe_gather_rows(plan: MoEPlan, src: torch.Tensor, div: int) -> torch.Tensor:
     n_exp = plan.offsets.numel() - 1
     st = _lib("moe_tc").dlgo_moe_gather_rows(
         _ptr(src), _ll(src.stride(0) * src.element_size()), _ptr(dst), _i(src.shape[1] * src.element_size()),
-        _ptr(plan.sorted_pair), _ptr(plan.offsets[n_exp:]), _i(div), _i(plan.pairs), _stream())
+        _ptr(plan.sorted_pair), _ptr(plan.offsets[n_exp:]), _i(div), _i(plan.pairs), _ptr(scale), _stream())
     _check(st, "moe_gather_rows")
     return dst
 
@@ -1095,30 +1112,30 @@ def moe_gemm_tc(plan: MoEPlan, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
     return out
 
 
-def moe_scale_rows(h: torch.Tensor, wt: torch.Tensor) -> tuple:
-    """For experts whose weight multiplies their input: (rows [T * top, d] with ``rows[t * top + k] = wt[t, k] *
-    h[t]`` in ``h``'s type, ones [T, top] fp32 as the weights the combine then uses)."""
+def moe_scale_rows(h: torch.Tensor, wt: torch.Tensor) -> torch.Tensor:
+    """For experts whose weight multiplies their input: rows [T * top, d] with ``rows[t * top + k] = wt[t, k] *
+    h[t]`` in ``h``'s type (the product in fp32)."""
     _need(wt, torch.float32, "wt")
     if h.dim() != 2 or h.stride(1) != 1 or wt.dim() != 2 or wt.shape[0] != h.shape[0]:
         raise KernelError("moe_scale_rows: h [T, d] with unit inner stride, wt [T, top]")
     T, d = h.shape
     top = wt.shape[1]
     rows = torch.empty((T * top, d), dtype=h.dtype, device=h.device)
-    ones = torch.empty((T, top), dtype=torch.float32, device=h.device)
     st = _lib("moe").dlgo_moe_scale_rows(_ptr(h), _i(dtype_code(h.dtype)), _i(h.stride(0)), _ptr(wt), _ptr(rows),
-                                         _ptr(ones), _i(T * top), _i(d), _i(top), _stream())
+                                         _i(T * top), _i(d), _i(top), _stream())
     _check(st, "moe_scale_rows")
-    return rows, ones
+    return rows
 
 
 def moe_combine(y: torch.Tensor, pair_out: Optional[torch.Tensor], h: torch.Tensor, idx: torch.Tensor,
-                wt: torch.Tensor, n_experts: int, shared: Optional[torch.Tensor] = None,
+                wt: Optional[torch.Tensor], n_experts: int, shared: Optional[torch.Tensor] = None,
                 gate: Optional[torch.Tensor] = None) -> None:
     """``y[t] += sum_k wt[t, k] * (pair_out[t * top + k] if idx[t, k] < n_experts else h[t]) + gate[t] * shared[t]``
-    (sums in fp32; ``gate`` None: 1; ``pair_out`` fp32 or of ``h``'s type)."""
+    (sums in fp32; ``gate`` None: 1; ``wt`` None: every weight 1; ``pair_out`` fp32 or of ``h``'s type)."""
     _need(y, torch.float32, "y")
     _need(idx, torch.int32, "idx")
-    _need(wt, torch.float32, "wt")
+    if wt is not None:
+        _need(wt, torch.float32, "wt")
     T, d = y.shape
     top = idx.shape[1]
     if h.dim() != 2 or h.stride(1) != 1 or tuple(h.shape) != (T, d):

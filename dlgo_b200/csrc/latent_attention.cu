@@ -534,6 +534,7 @@ latent_out_kernel(const float* __restrict__ parts, const T* __restrict__ w_v, co
       float L = sink ? expf(sk - M) : 0.f;
       for (int q = 0; q < n_slices; ++q) L = fmaf(__shfl_sync(0xffffffffu, ls, q), __shfl_sync(0xffffffffu, es, q), L);
       const float f = es / L;
+#pragma unroll 4      // (several columns' fetches in flight: the loop is a chain of memory latencies otherwise)
       for (int r0 = 0; r0 < rank; r0 += 32) {                  // (the whole warp stays in the loop: it shuffles)
         const int r = r0 + lane;
         const float* col = p + 2 + (r < rank ? r : 0);          // (no branch between the fetches)

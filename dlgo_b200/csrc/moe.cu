@@ -511,7 +511,7 @@ moe_combine_kernel(float* __restrict__ y, const P* __restrict__ pair_out, const 
   for (int c = 0; c < W; ++c) acc[c] = 0.f;
   for (int k = 0; k < top; ++k) {
     const int e = idx[(size_t)t * top + k];
-    const float wk = wt[(size_t)t * top + k];
+    const float wk = wt != nullptr ? wt[(size_t)t * top + k] : 1.f;
     float v[W];
     if (e < n_experts) {
       const P* src = pair_out + ((size_t)t * top + k) * d + i;
@@ -543,9 +543,9 @@ moe_combine_kernel(float* __restrict__ y, const P* __restrict__ pair_out, const 
 // ------------------------------------------------------------------------------ weights on the input
 // For experts whose weight multiplies their INPUT (y = sum_k expert_k(w_k h), which is not w_k expert_k(h) once
 // an expert is not linear): one row per (token, choice) pair, rows[t * top + k] = w[t][k] * h[t] in the run's
-// type (the product in fp32), and ones[t * top + k] = 1 as the weights the combine then uses.
+// type (the product in fp32); the combine then adds the experts' results as they are (no weights).
 template <typename T>
-__global__ void moe_scale_rows_kernel(const T* h, int ldh, const float* wt, T* rows, float* ones, int d, int top) {
+__global__ void moe_scale_rows_kernel(const T* h, int ldh, const float* wt, T* rows, int d, int top) {
   pdl_launch_dependents();
   const int p = blockIdx.x;
   pdl_wait();
@@ -553,7 +553,6 @@ __global__ void moe_scale_rows_kernel(const T* h, int ldh, const float* wt, T* r
   const T* src = h + (size_t)(p / top) * ldh;
   T* dst = rows + (size_t)p * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_float<T>(w * to_float(src[i]));
-  if (threadIdx.x == 0) ones[p] = 1.0f;
 }
 
 template <typename T, typename P>
@@ -674,17 +673,17 @@ DLGO_EXPORT int dlgo_moe_gemm(int kind, int dtype, const void* A, long long lda,
 }
 
 // pair_out: the experts' results [tokens * top, d], fp32 (pair_f32) or of h's type
-DLGO_EXPORT int dlgo_moe_scale_rows(const void* h, int dtype, int ldh, const float* wt, void* rows, float* ones,
-                                    int pairs, int d, int top, cudaStream_t stream) {
+DLGO_EXPORT int dlgo_moe_scale_rows(const void* h, int dtype, int ldh, const float* wt, void* rows, int pairs, int d,
+                                    int top, cudaStream_t stream) {
   if (pairs <= 0) return DLGO_OK;
   if (d <= 0 || top <= 0) return DLGO_ERR_SIZE;
   const int threads = d >= 1024 ? 256 : 128;
   if (dtype == DLGO_F32)
     launch_kernel(moe_scale_rows_kernel<float>, dim3(pairs), dim3(threads), 0, stream, (const float*)h, ldh, wt,
-                  (float*)rows, ones, d, top);
+                  (float*)rows, d, top);
   else if (dtype == DLGO_BF16)
     launch_kernel(moe_scale_rows_kernel<__nv_bfloat16>, dim3(pairs), dim3(threads), 0, stream, (const __nv_bfloat16*)h,
-                  ldh, wt, (__nv_bfloat16*)rows, ones, d, top);
+                  ldh, wt, (__nv_bfloat16*)rows, d, top);
   else
     return DLGO_ERR_DTYPE;
   return launch_status();

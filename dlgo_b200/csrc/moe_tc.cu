@@ -438,14 +438,27 @@ moe_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 // that belong to an expert (16 bytes per thread and step).
 __global__ void __launch_bounds__(256)
 moe_gather_rows_kernel(const uint4* __restrict__ src, long long src_ld16, uint4* __restrict__ dst, int row16,
-                       const int* __restrict__ sorted_pair, const int* __restrict__ total, int div, int max_rows) {
+                       const int* __restrict__ sorted_pair, const int* __restrict__ total, int div, int max_rows,
+                       const float* __restrict__ pair_scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int n = min(*total, max_rows);
   const long long items = (long long)n * row16;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < items; i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / row16), c = (int)(i - (long long)r * row16);
-    dst[(long long)r * row16 + c] = src[(long long)(sorted_pair[r] / div) * src_ld16 + c];
+    const int pair = sorted_pair[r];
+    uint4 v = src[(long long)(pair / div) * src_ld16 + c];
+    if (pair_scale != nullptr) {
+      // bfloat16 rows whose pair brings a factor: the product in fp32, rounded once
+      const float f = pair_scale[pair];
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = __bfloat1622float2(h[k]);
+        h[k] = __floats2bfloat162_rn(a.x * f, a.y * f);
+      }
+    }
+    dst[(long long)r * row16 + c] = v;
   }
 }
 
@@ -606,10 +619,11 @@ DLGO_EXPORT int dlgo_moe_gemm_tc(const void* A, long long a_rows, long long lda,
   return launch_grouped<128>(ma, mb, p, max_tiles, 66, stream);
 }
 
-// dst[r][:] = src[sorted_pair[r] / div][:] for the rows that belong to an expert; rows of `row_bytes` (a multiple of 16)
+// dst[r][:] = src[sorted_pair[r] / div][:] for the rows that belong to an expert; rows of `row_bytes` (a multiple of 16).
+// `pair_scale` (fp32, one number per pair; rows of bfloat16 only): the row is multiplied by its pair's number.
 DLGO_EXPORT int dlgo_moe_gather_rows(const void* src, long long src_ld_bytes, void* dst, int row_bytes,
                                      const int* sorted_pair, const int* total, int div, int max_rows,
-                                     cudaStream_t stream) {
+                                     const float* pair_scale, cudaStream_t stream) {
   if (max_rows <= 0) return DLGO_OK;
   if (row_bytes <= 0 || row_bytes % 16 || src_ld_bytes % 16 || div <= 0 || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15))
     return DLGO_ERR_ALIGN;
@@ -617,7 +631,7 @@ DLGO_EXPORT int dlgo_moe_gather_rows(const void* src, long long src_ld_bytes, vo
   long long want = (items + 255) / 256;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   launch_kernel(moe_gather_rows_kernel, dim3(blocks), dim3(256), 0, stream, (const uint4*)src, src_ld_bytes / 16,
-                (uint4*)dst, row_bytes / 16, sorted_pair, total, div, max_rows);
+                (uint4*)dst, row_bytes / 16, sorted_pair, total, div, max_rows, pair_scale);
   return launch_status();
 }
 

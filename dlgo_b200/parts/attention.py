@@ -468,6 +468,7 @@ class ShortConvAttention(GQAAttention):
     manager's window bookkeeping is for sliding windows.  ``names``: tensor names below the part's prefix."""
 
     head_multiple = 8
+    can_defer_bias = True       # a caller may add :attr:`output_bias` itself, in its next pass over the result
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, qk_dim: int, v_dim: int, scale: float,
                  bias: bool = False, conv_taps: Optional[int] = None, window: Optional[int] = None,
@@ -499,7 +500,7 @@ class ShortConvAttention(GQAAttention):
         self.names.update(names or {})
         self.w_in: Optional[Linear] = None        # rows q | k | v
         self.b_in: Optional[torch.Tensor] = None
-        self.b_out: Optional[torch.Tensor] = None
+        self.output_bias: Optional[torch.Tensor] = None
         self.w_taps: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -535,13 +536,15 @@ class ShortConvAttention(GQAAttention):
         self.wo = Linear(wo.contiguous(), runtime)
         if self.bias:       # added in fp32: to the projection's fp32 result, and to the fp32 sum the mixer adds into
             self.b_in = torch.cat([get(n[key + "_bias"]).to(torch.float32) for key in ("q", "k", "v")]).contiguous()
-            self.b_out = get(n["out_bias"]).to(torch.float32).contiguous()
+            self.output_bias = get(n["out_bias"]).to(torch.float32).contiguous()
         if self.taps > 1:
             self.w_taps = torch.cat([get(n[key + "_conv"]).to(torch.float32) for key in ("q", "k", "v")],
                                     dim=0).contiguous()
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: Any, cache: Any,
-                state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding]) -> None:
+                state: Optional[torch.Tensor], positions: Mapping[str, PositionEncoding],
+                defer_bias: bool = False) -> None:
+        """``defer_bias``: the caller adds :attr:`output_bias` itself."""
         T = ctx.n_tokens
         act = self.w_in.weight.dtype
         freq, rot, amplitude = None, 0, 1.0
@@ -557,14 +560,23 @@ class ShortConvAttention(GQAAttention):
             state = state.view(state.shape[0], -1)
             tiles, n_tiles, _ = ctx.tiles(1 if ctx.decode else _WHOLE_SEQUENCE)
         decode_kernel, mma, n_splits, scratch, counters, pages = self._decode_plan(ctx, cache, act)
-        proj = self.w_in(x, STORE_F32)
+        n_cols = self.w_in.out_features
+        clear = (ctx.decode and _QKV_SUM and self.w_in.sums_slices_at_memory(T) and
+                 K.conv_rope_append_clears(self.qk_dim, self.v_dim, self.head_dim, n_cols, self.taps))
+        if clear:
+            # decoding: the projection's K-slices add themselves into one fp32 sum that is zero between steps; the
+            # kernel behind it reads a token's row once and leaves zeros
+            proj = ctx.zeros(f"qkv_conv_sum{n_cols}", T * n_cols, torch.float32)[:T * n_cols].view(T, n_cols)
+            self.w_in(x, ADD_F32, proj)
+        else:
+            proj = self.w_in(x, STORE_F32)
         q = K.conv_rope_append(proj, self.b_in, self.w_taps, state, freq, rot, amplitude, ctx.token_pos, ctx.token_seq,
                                ctx.seq_slot, cache.page_table, cache.keys, cache.values, self.num_heads,
-                               self.num_kv_heads, self.qk_dim, self.v_dim, tiles, n_tiles, cache.writes)
+                               self.num_kv_heads, self.qk_dim, self.v_dim, tiles, n_tiles, cache.writes, ctx.decode, clear)
         out = torch.empty((T, self.q_dim), dtype=act, device=x.device)
         self._attend(q, ctx, cache, out, decode_kernel, mma, n_splits, scratch, counters, pages)
-        if self.b_out is not None:
-            K.bias_act(residual, self.b_out, K.ACT_NONE, torch.float32, in_place=True)
+        if self.output_bias is not None and not defer_bias:
+            K.bias_act(residual, self.output_bias, K.ACT_NONE, torch.float32, in_place=True)
         self.wo(out, ADD_F32, residual)
 
 

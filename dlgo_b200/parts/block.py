@@ -267,9 +267,17 @@ class ResidualGate(Part):
         self.proj = Linear(get(self.names["weight"]), runtime)
         self.bias = get(self.names["bias"]).to(torch.float32).contiguous()      # added to the fp32 logits
 
-    def logits(self, h: torch.Tensor) -> torch.Tensor:
-        """``W h`` as fp32 [T, size]; bias and sigmoid belong to the pass that applies the gate."""
-        return self.proj(h, K.EPI_STORE_F32)
+    def logits(self, h: torch.Tensor, ctx: Any = None) -> tuple:
+        """(``W h`` as fp32 [T, size], whether the reader must leave zeros behind); bias and sigmoid belong to the
+        pass that applies the gate.  With few tokens the contraction's K-slices add themselves into a sum that is
+        zero between uses (the reader clears it), which spares the slices' meeting in a workspace."""
+        T = h.shape[0]
+        if ctx is not None and self.proj.sums_slices_at_memory(T):
+            n = T * self.size
+            z = ctx.zeros(f"gate_logits{self.size}", n, torch.float32)[:n].view(T, self.size)
+            self.proj(h, K.EPI_ADD_F32, z)
+            return z, True
+        return self.proj(h, K.EPI_STORE_F32), False
 
 
 class DepthAverage(Part):
@@ -356,21 +364,25 @@ class GatedPreNormBlock(Block):
         nn = self._next_norm
         tail = dict(norm_w=nn.weight, eps=nn.eps, out_dtype=dtype) if nn is not None else {}
         for i, (part, norm, gate) in enumerate(self.sublayers):
+            # (a sublayer that ends with a bias may leave it to the pass that applies the gate)
+            defer = {"defer_bias": True} if getattr(part, "can_defer_bias", False) else {}
             if part is self.mixer:
-                part.forward(x, y, ctx, cache, state, positions)
+                part.forward(x, y, ctx, cache, state, positions, **defer)
             else:
-                part.forward(x, y, ctx)
+                part.forward(x, y, ctx, **defer)
             ctx.settle(y)
-            logits = gate.logits(x) if gate is not None else None
+            logits, clear = gate.logits(x, ctx) if gate is not None else (None, False)
             bias = gate.bias if gate is not None else None
+            y_bias = part.output_bias if defer else None
             if i < last:
                 nxt = self.sublayers[i + 1][1]
-                x = K.gated_residual(residual, y, logits, bias, norm_w=nxt.weight, eps=nxt.eps, out_dtype=dtype)
+                x = K.gated_residual(residual, y, logits, bias, y_bias=y_bias, norm_w=nxt.weight, eps=nxt.eps,
+                                     out_dtype=dtype, clear_gate=clear)
             elif avg is not None:
-                x = K.gated_residual(residual, y, logits, bias, history=history, depth=avg.depth, average=avg.weights,
-                                     **tail)
+                x = K.gated_residual(residual, y, logits, bias, y_bias=y_bias, history=history, depth=avg.depth,
+                                     average=avg.weights, clear_gate=clear, **tail)
             else:
-                x = K.gated_residual(residual, y, logits, bias, **tail)
+                x = K.gated_residual(residual, y, logits, bias, y_bias=y_bias, clear_gate=clear, **tail)
         if nn is not None:
             ctx.normed_ahead = (residual, nn, x)
 

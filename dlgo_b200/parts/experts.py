@@ -170,11 +170,16 @@ class RoutedExperts(FeedForward):
                                            self.group_count, self.group_keep, self.sigmoid_scores, self.renormalize,
                                            plan=(self.num_experts, tile_rows), logit_bias=self.b_logit)
         pair_out = None
-        src, div = x, self.top
+        src, div, scale = x, self.top, None
         if self.weight_on_input:
-            # a row per pair, already multiplied by its weight; the combine then adds the experts' results as they are
-            src, wt = K.moe_scale_rows(x, wt)
-            div = 1
+            # an expert reads its row multiplied by the pair's weight: on the tensor-core path the copy into sorted
+            # order multiplies on its way, else a pass makes a row per pair; the combine then adds the experts'
+            # results as they are
+            if on_tc:
+                scale = wt
+            else:
+                src, div = K.moe_scale_rows(x, wt), 1
+            wt = None
         if self.num_experts:
             # (gated: the first contraction leaves gate and up values side by side; silu(gate) * up is formed on the
             # tensor-core kernel's accumulator where the rows alternate in blocks, else by a pass of its own)
@@ -185,7 +190,7 @@ class RoutedExperts(FeedForward):
             pair_out = torch.empty((pairs, d), dtype=x.dtype, device=x.device)    # (sums of these stay fp32)
             if on_tc:
                 # bfloat16: the tokens' rows copied into sorted order, then both contractions on tcgen05
-                rows = K.moe_gather_rows(plan, src, div)
+                rows = K.moe_gather_rows(plan, src, div, scale)
                 K.moe_gemm_tc(plan, rows, self.w_up, hidden, False, K.MOE_ACT_SWIGLU if fused else act)
                 if self.gated and not fused:
                     hidden = K.swiglu(hidden, block=self.gate_block)

@@ -187,6 +187,12 @@ def test_gate_depth_average_and_norm(act_dtype):
         out = K.gated_residual(xd, yd, gl.to(DEV)[:, :d], gb.to(DEV), norm_w=w.to(DEV), eps=eps, out_dtype=act_dtype)
         assert torch.allclose(xd.cpu().double(), want_x, rtol=1e-6, atol=1e-6) and not yd.any()
         assert torch.allclose(out.float().cpu().double(), P.rms_norm(want_x, w.double(), eps), **loose)
+        # a bias that the sublayer left to this pass joins its result before the gate
+        yb = torch.randn(d, generator=g)
+        xd, yd = x.to(DEV), y.to(DEV)
+        K.gated_residual(xd, yd, gl.to(DEV)[:, :d], gb.to(DEV), y_bias=yb.to(DEV))
+        biased = x.double() + torch.sigmoid(gl[:, :d].double() + gb.double()) * (y.double() + yb.double())
+        assert torch.allclose(xd.cpu().double(), biased, rtol=1e-6, atol=1e-6) and not yd.any()
         # gate, add, then the average over three entries of which the sum is the last
         xd, yd, hd = x.to(DEV), y.to(DEV), hist.to(DEV)
         assert K.gated_residual(xd, yd, gl.to(DEV)[:, :d], gb.to(DEV), history=hd, depth=3, average=avg.to(DEV)) is None
@@ -224,9 +230,20 @@ def test_rows_multiplied_by_their_experts_weights(act_dtype):
     g = torch.Generator().manual_seed(4)
     h = torch.randn(11, 40, generator=g).to(act_dtype)
     wt = torch.rand(11, 3, generator=g)
-    rows, ones = K.moe_scale_rows(h.to(DEV), wt.to(DEV))
+    rows = K.moe_scale_rows(h.to(DEV), wt.to(DEV))
     want = (wt[:, :, None] * h.float()[:, None, :]).reshape(33, 40).to(act_dtype)
-    assert torch.equal(rows.cpu(), want) and torch.equal(ones.cpu(), torch.ones(11, 3))
+    assert torch.equal(rows.cpu(), want)
+    if act_dtype == torch.bfloat16:
+        # the same product on the way into sorted order (the tensor-core experts' copy)
+        idx = torch.randint(0, 4, (11, 3), generator=g, dtype=torch.int32)
+        plan = K.moe_plan(idx.to(DEV), 4, K.MOE_TC_ROWS)
+        got = K.moe_gather_rows(plan, h.to(DEV), 3, scale=wt.to(DEV)).cpu()
+        assert torch.equal(got, want[plan.sorted_pair.cpu().long()])
+    # weights of one in the combine
+    y = torch.zeros(11, 40, device=DEV)
+    pair_out = torch.randn(33, 40, generator=g).to(act_dtype)
+    K.moe_combine(y, pair_out.to(DEV), h.to(DEV), torch.zeros(11, 3, dtype=torch.int32, device=DEV), None, 1)
+    assert torch.allclose(y.cpu(), pair_out.float().view(11, 3, 40).sum(1), atol=1e-5)
 
 
 # --------------------------------------------------- mechanisms alone: one-layer models that hold nothing else
