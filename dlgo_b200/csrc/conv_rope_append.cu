@@ -193,6 +193,119 @@ __global__ void __launch_bounds__(256) conv_rope_append_pairs_kernel(ConvAppendA
   }
 }
 
+// Many tokens (prompts): a block walks CT_TOKENS consecutive rows, a thread keeping its two channels' last NT - 1
+// values in registers, so that a row of proj is read once (not once per tap) and taps, bias and the head's place are
+// looked up once per block.  All of the tile's own values are fetched before the walk begins.  The state is left to
+// the second launch.
+constexpr int CT_TOKENS = 8;
+
+template <typename T, int NT>
+__global__ void __launch_bounds__(128) conv_rope_append_tiles_kernel(ConvAppendArgs a) {
+  pdl_launch_dependents();
+  const int C = (a.H + a.G) * a.dk + a.G * a.dv;
+  const int pairs = a.hd >> 1;
+  const int idx = blockIdx.y * blockDim.x + threadIdx.x;
+  const int t0 = blockIdx.x * CT_TOKENS;
+  const int nt = min(CT_TOKENS, a.T - t0);
+  if (idx >= (a.H + 2 * a.G) * pairs) return;
+  const int head = idx / pairs, e = (idx - head * pairs) * 2;
+  int kind, hh, width, c0;
+  if (head < a.H) { kind = 0; hh = head; width = a.dk; c0 = hh * a.dk; }
+  else if (head < a.H + a.G) { kind = 1; hh = head - a.H; width = a.dk; c0 = a.H * a.dk + hh * a.dk; }
+  else { kind = 2; hh = head - a.H - a.G; width = a.dv; c0 = (a.H + a.G) * a.dk + hh * a.dv; }
+  const bool live = e < width;                 // (else: zeros behind the head's own numbers)
+  const int c = c0 + (live ? e : 0);
+  const float2 b = (live && a.bias) ? __ldg(reinterpret_cast<const float2*>(a.bias + c)) : make_float2(0.f, 0.f);
+  float w0[NT], w1[NT];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    w0[j] = (live && a.taps) ? __ldg(a.taps + (size_t)c * NT + j) : (j == NT - 1 ? 1.f : 0.f);
+    w1[j] = (live && a.taps) ? __ldg(a.taps + (size_t)(c + 1) * NT + j) : (j == NT - 1 ? 1.f : 0.f);
+  }
+  const bool turns = kind < 2 && live && e < a.rot;
+  const float f = turns ? a.freq[e >> 1] : 0.f;
+  // the tile's sequences and positions: the step's own inputs, fetched before the wait
+  int seqs[CT_TOKENS], poss[CT_TOKENS];
+#pragma unroll
+  for (int i = 0; i < CT_TOKENS; ++i) {
+    seqs[i] = i < nt ? a.token_seq[t0 + i] : -1;
+    poss[i] = i < nt ? a.token_pos[t0 + i] : 0;
+  }
+  pdl_wait();
+  float2 cur[CT_TOKENS];
+#pragma unroll
+  for (int i = 0; i < CT_TOKENS; ++i) {
+    cur[i] = make_float2(0.f, 0.f);
+    if (live && i < nt) {
+      cur[i] = *reinterpret_cast<const float2*>(a.proj + (size_t)(t0 + i) * a.ld + c);
+      cur[i].x += b.x;
+      cur[i].y += b.y;
+    }
+  }
+  float2 win[NT > 1 ? NT - 1 : 1];
+  int prev_seq = -1, slot = 0;
+#pragma unroll
+  for (int i = 0; i < CT_TOKENS; ++i) {
+    if (i >= nt) break;
+    const int t = t0 + i;
+    const int seq = seqs[i];
+    const int pos = poss[i];
+    if (seq != prev_seq) {
+      // the sequence's rows before this one: of this step (as far as the taps reach), else of its state
+      slot = a.seq_slot[seq];
+      prev_seq = seq;
+      if (NT > 1 && live) {
+        int n_in = 0;
+        while (n_in < NT - 1 && t - n_in - 1 >= 0 && a.token_seq[t - n_in - 1] == seq) ++n_in;
+        const float* st = a.state + (size_t)slot * (NT - 1) * C;
+#pragma unroll
+        for (int j = 0; j < NT - 1; ++j) {
+          const int back = NT - 1 - j;
+          if (back <= n_in) {
+            win[j] = *reinterpret_cast<const float2*>(a.proj + (size_t)(t - back) * a.ld + c);
+            win[j].x += b.x;
+            win[j].y += b.y;
+          } else {
+            win[j] = *reinterpret_cast<const float2*>(st + (size_t)(NT - 1 - (back - n_in)) * C + c);
+          }
+        }
+      }
+    }
+    float2 y = make_float2(w0[NT - 1] * cur[i].x, w1[NT - 1] * cur[i].y);
+    if (NT > 1) {
+#pragma unroll
+      for (int j = 0; j < NT - 1; ++j) {
+        y.x = fmaf(w0[j], win[j].x, y.x);
+        y.y = fmaf(w1[j], win[j].y, y.y);
+      }
+#pragma unroll
+      for (int j = 0; j + 1 < NT - 1; ++j) win[j] = win[j + 1];
+      win[NT - 2 >= 0 ? NT - 2 : 0] = cur[i];
+    }
+    if (!live) y = make_float2(0.f, 0.f);
+    if (turns) {
+      float sn, cs;
+      sincosf((float)pos * f, &sn, &cs);
+      sn *= a.amplitude;
+      cs *= a.amplitude;
+      const float p0 = y.x, p1 = y.y;
+      y.x = p0 * cs - p1 * sn;
+      y.y = p1 * cs + p0 * sn;
+    }
+    T* dst = nullptr;
+    if (kind == 0) {
+      dst = (T*)a.q_out + ((size_t)t * a.H + hh) * a.hd;
+    } else if (a.write_cache) {
+      const int page = a.page_table[(size_t)slot * a.max_pages + pos / a.page_size];
+      T* pages = (T*)(kind == 1 ? a.kpages : a.vpages);
+      if (page >= 0) dst = pages + (((size_t)page * a.G + hh) * a.page_size + pos % a.page_size) * a.hd;
+    }
+    if (dst == nullptr) continue;
+    if (sizeof(T) == 2) *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(y.x, y.y);
+    else *reinterpret_cast<float2*>(dst + e) = y;
+  }
+}
+
 // The state after the step: a block per sequence of the step (tiles [n, 3]: sequence, its first packed token,
 // its token count), a thread per channel, which reads all it needs before it writes.
 __global__ void conv_state_keep_kernel(const float* proj, int ld, const float* __restrict__ bias, int n_taps,
@@ -250,7 +363,20 @@ DLGO_EXPORT int dlgo_conv_rope_append(const float* proj, int ld, int T, const fl
   // (only the kernel for even sizes and few taps clears proj: dlgo_conv_rope_append_clears says whether it runs)
   if (clear_proj && !(all_alone && even && n_taps <= 4)) return DLGO_ERR_SIZE;
   bool kept = false;      // whether tokens alone in their sequence keep the state themselves
-  if (even && n_taps <= 4) {
+  if (even && n_taps <= 4 && T > 64 && !all_alone) {
+    // prompts: tiles of tokens, the state left to the second launch
+    const dim3 grid((T + CT_TOKENS - 1) / CT_TOKENS, ((H + 2 * G) * (hd >> 1) + 127) / 128);
+#define DLGO_CONV_TILES(NT)                                                                                            \
+  do {                                                                                                                 \
+    if (dtype == DLGO_F32) launch_kernel(conv_rope_append_tiles_kernel<float, NT>, grid, dim3(128), 0, stream, a);     \
+    else launch_kernel(conv_rope_append_tiles_kernel<__nv_bfloat16, NT>, grid, dim3(128), 0, stream, a);               \
+  } while (0)
+    if (n_taps == 1) DLGO_CONV_TILES(1);
+    else if (n_taps == 2) DLGO_CONV_TILES(2);
+    else if (n_taps == 3) DLGO_CONV_TILES(3);
+    else DLGO_CONV_TILES(4);
+#undef DLGO_CONV_TILES
+  } else if (even && n_taps <= 4) {
     const int th = work >= 256 ? 256 : 128;
     a.keep_alone = kept = n_taps > 1;
     a.clear_proj = clear_proj && all_alone;
