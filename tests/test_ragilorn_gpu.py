@@ -266,7 +266,7 @@ def check_model(cfg, w, dtype, what, n=150, start=70, seed=6):
 @pytest.mark.parametrize("H, G, dk, dv, rot, conv, chunk", [
     (6, 3, 24, 40, 12, 3, 37), (4, 4, 16, 8, 16, None, None), (5, 1, 40, 16, 8, 2, 150), (4, 2, 64, 64, 32, 4, 70),
     (2, 1, 32, 128, 32, 4, 64), (8, 2, 128, 64, 64, 4, 129), (3, 3, 20, 12, 0, 5, 2), (2, 2, 12, 100, 4, 8, 65),
-    (6, 1, 128, 64, 64, 4, 96), (2, 1, 64, 64, 64, None, 1)])
+    (5, 1, 128, 48, 96, 3, 88), (2, 1, 64, 64, 64, None, 1)])
 def test_attention_alone(H, G, dk, dv, rot, conv, chunk, dtype):
     cfg = one_layer(att(H, G, dk, dv, 0.9 * dk ** -0.5, rot, 20000.0, yarn(2.0, 64) if rot else None, conv, chunk))
     w = make_weights(cfg, dk + dv + (chunk or 0))
@@ -275,7 +275,7 @@ def test_attention_alone(H, G, dk, dv, rot, conv, chunk, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H, dk, r, dv, R", [(3, 24, 8, 20, 40), (1, 8, 4, 40, 9), (4, 32, 32, 64, 96), (2, 64, 64, 128, 128),
-                                             (8, 64, 32, 80, 96), (2, 16, 16, 24, 18), (2, 96, 32, 128, 160)])
+                                             (6, 64, 16, 72, 112), (2, 16, 16, 24, 18), (2, 96, 32, 128, 160)])
 def test_latent_attention_alone(H, dk, r, dv, R, dtype):
     cfg = one_layer(lat(H, dk, r, dv, R, 0.9 * (dk + r) ** -0.5, 3000.0, yarn(4.0, 32)))
     w = make_weights(cfg, dk + dv + R)
@@ -320,7 +320,7 @@ def standing_out(cfg, w):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H, G, dk, dv, size", [(2, 1, 24, 16, 100), (4, 2, 64, 64, 131), (2, 2, 32, 64, 64), (2, 1, 128, 64, 96)])
+@pytest.mark.parametrize("H, G, dk, dv, size", [(2, 1, 24, 16, 100), (4, 2, 64, 64, 131), (2, 2, 32, 64, 64), (2, 1, 128, 64, 88)])
 def test_a_key_just_inside_and_just_outside_the_chunk(H, G, dk, dv, size, dtype):
     """One key carries the answer.  The query sees it as the first position of its own chunk and no longer as the
     last of the chunk before, in a prompt and decoded, wherever the edge lies among the pages; chunks count from
