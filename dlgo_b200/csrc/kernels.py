@@ -411,6 +411,46 @@ def latent_attention_few(q: torch.Tensor, w_k: torch.Tensor, w_v: torch.Tensor, 
     return out
 
 
+def latent_attention_tiles_takes(dtype: torch.dtype, num_heads: int, rank: int) -> bool:
+    """Whether the few-token kernels that serve all heads of a token from one tile of keys take these sizes."""
+    if dtype not in (torch.float32, torch.bfloat16):
+        return False
+    return bool(_lib("latent_attention").dlgo_latent_attention_tiles_takes(_i(dtype_code(dtype)), _i(num_heads), _i(rank)))
+
+
+def latent_attention_tiles(q: torch.Tensor, w_k: torch.Tensor, w_v: torch.Tensor, sink: Optional[torch.Tensor],
+                           pages: torch.Tensor, page_table: torch.Tensor, seq_slot: torch.Tensor,
+                           token_seq: torch.Tensor, token_pos: torch.Tensor, num_heads: int, qk_dim: int, v_dim: int,
+                           scale: float, window: int, n_slices: int, q_lat: torch.Tensor,
+                           parts: torch.Tensor) -> torch.Tensor:
+    """:func:`latent_attention_few` with every latent row read once per token instead of once per head: four
+    launches (queries into latent space; tiles of 32 keys in shared memory serving all heads, a block per token and
+    slice of the keys; the slices' meeting; out through ``w_v``).  Same arguments and scratch."""
+    _need(pages, None, "pages")
+    _need(w_k, pages.dtype, "w_k")
+    _need(w_v, pages.dtype, "w_v")
+    if q.dtype not in (torch.float32, pages.dtype) or q.dim() != 2 or q.stride(1) != 1:
+        raise KernelError("latent_attention_tiles: q must be 2-D, float32 or the cache's type, with unit inner stride")
+    if sink is not None:
+        _need(sink, torch.float32, "sink")
+    for n, t in (("page_table", page_table), ("seq_slot", seq_slot), ("token_seq", token_seq), ("token_pos", token_pos)):
+        _need(t, torch.int32, n)
+    T, rank = q.shape[0], pages.shape[-1]
+    if tuple(w_k.shape) != (num_heads * qk_dim, rank) or tuple(w_v.shape) != (num_heads * v_dim, rank):
+        raise KernelError("latent_attention_tiles: the up-projections do not fit heads, sizes and rank")
+    if q_lat.dtype != torch.float32 or q_lat.numel() < T * num_heads * rank or parts.dtype != torch.float32 or \
+            parts.numel() < T * num_heads * n_slices * (rank + 2):
+        raise KernelError("latent_attention_tiles: scratch too small")
+    out = torch.empty((T, num_heads * v_dim), dtype=pages.dtype, device=q.device)
+    st = _lib("latent_attention").dlgo_latent_attention_tiles(
+        _ptr(q), _i(1 if q.dtype == torch.float32 else 0), _i(q.stride(0)), _ptr(w_k), _ptr(w_v), _ptr(sink),
+        _ptr(pages), _i(dtype_code(pages.dtype)), _ptr(page_table), _i(page_table.shape[1]), _i(pages.shape[-2]),
+        _ptr(seq_slot), _ptr(token_seq), _ptr(token_pos), _ptr(out), _i(out.stride(0)), _i(T), _i(num_heads),
+        _i(qk_dim), _i(v_dim), _i(rank), _f(scale), _i(window), _i(n_slices), _ptr(q_lat), _ptr(parts), _stream())
+    _check(st, "latent_attention_tiles", 4)
+    return out
+
+
 def latent_gather(pages: torch.Tensor, page_table: torch.Tensor, tmp_pages: torch.Tensor, n_tmp: int,
                   seq_slot: torch.Tensor) -> torch.Tensor:
     """Rows [n_tmp * page, rank] of the cached latents of the pages listed in ``tmp_pages`` [n_tmp, 3]

@@ -588,6 +588,291 @@ static int launch_latent_few(const void* q, int q_is_f32, int ldq, const void* w
   return launch_status();
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Few tokens, every head of a token in one block: the three launches above read every latent row once per head.
+// Here a block owns (token, slice of the visible keys) and ALL heads: a tile of 32 latent rows is brought into
+// shared memory once (fp32, rows padded so that a lane per key reads 16-byte pieces without bank conflicts) and
+// serves every head.  A warp owns HW heads; for the scores a lane owns a key (its dot products with the HW query
+// latents, which sit in shared memory and are read as broadcasts), for the weighted latent a lane owns RC columns
+// of the row (registers: HW x RC sums).  Online softmax per head in fp32.  Leaves (max, sum, weighted latent) per
+// (token, head, slice) in the format of latent_partial.  Then
+//   combine  a block per (token, head): the slices meet in slice order, the sink joins the denominator; leaves the
+//            normalised weighted latent (fp32)
+//   project  a block per (head, 16 value columns): two rows of Wv_h per warp in registers, every token's weighted
+//            latent read once per block
+constexpr int LT_KEYS = 32, LT_WARPS = 8;
+
+__host__ __device__ inline int lt_row_stride(int rank) { return rank + ((rank & 7) == 0 ? 4 : 8); }
+
+template <typename T, int RC, int HW>
+__global__ void __launch_bounds__(LT_WARPS * 32)
+latent_tile_kernel(const float* q_lat, const T* pages, const int* __restrict__ page_table, int max_pages,
+                   int page_size, const int* __restrict__ seq_slot, const int* __restrict__ token_seq,
+                   const int* __restrict__ token_pos, float* parts, int H, int rank, int n_slices, float scale,
+                   int window) {
+  constexpr int V = Vec16<T>::V;
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) float lt_smem[];
+  const int RS = lt_row_stride(rank);
+  float* q_s = lt_smem;                          // [H][rank]
+  float* c_s = q_s + (size_t)H * rank;           // [LT_KEYS][RS]
+  float* p_s = c_s + (size_t)LT_KEYS * RS;       // [LT_WARPS * HW][LT_KEYS]
+  const int t = blockIdx.x, slice = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = token_pos[t];
+  const int* table = page_table + (size_t)seq_slot[token_seq[t]] * max_pages;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int per = (pos - lo + n_slices) / n_slices;             // keys of a slice (the last may have fewer)
+  const int j0 = lo + slice * per, j1 = min(pos + 1, j0 + per);
+  const int h0 = warp * HW;
+  pdl_wait();
+  for (int i = threadIdx.x * 4; i < H * rank; i += LT_WARPS * 32 * 4)
+    *reinterpret_cast<float4*>(q_s + i) = *reinterpret_cast<const float4*>(q_lat + (size_t)t * H * rank + i);
+  float m[HW], l[HW], acc[HW][RC];
+#pragma unroll
+  for (int a = 0; a < HW; ++a) {
+    m[a] = -INFINITY;
+    l[a] = 0.f;
+#pragma unroll
+    for (int i = 0; i < RC; ++i) acc[a][i] = 0.f;
+  }
+  const int pieces = rank / V;                  // 16-byte pieces of a row
+  for (int jt = j0; jt < j1; jt += LT_KEYS) {
+    const int nk = min(LT_KEYS, j1 - jt);
+    __syncthreads();                            // (the tile before has been read; q_s is complete)
+    for (int idx = threadIdx.x; idx < LT_KEYS * pieces; idx += LT_WARPS * 32) {
+      const int k = idx / pieces, piece = idx - k * pieces;
+      float v[V];
+      if (k < nk) {
+        const int j = jt + k;
+        const T* row = pages + ((size_t)table[j / page_size] * page_size + j % page_size) * rank;
+        Vec16<T>::load(row + piece * V, v);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] = 0.f;
+      }
+      float* dst = c_s + (size_t)k * RS + piece * V;
+#pragma unroll
+      for (int e = 0; e < V; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+    }
+    __syncthreads();
+    if (h0 < H) {
+      // scores: this lane's key against the warp's heads
+      float s[HW];
+#pragma unroll
+      for (int a = 0; a < HW; ++a) s[a] = 0.f;
+      const float* crow = c_s + (size_t)lane * RS;
+      for (int r = 0; r < rank; r += 4) {
+        const float4 cv = *reinterpret_cast<const float4*>(crow + r);
+#pragma unroll
+        for (int a = 0; a < HW; ++a) {
+          const float4 qv = *reinterpret_cast<const float4*>(q_s + (size_t)min(h0 + a, H - 1) * rank + r);
+          s[a] = fmaf(qv.x, cv.x, s[a]);
+          s[a] = fmaf(qv.y, cv.y, s[a]);
+          s[a] = fmaf(qv.z, cv.z, s[a]);
+          s[a] = fmaf(qv.w, cv.w, s[a]);
+        }
+      }
+      float corr[HW];
+#pragma unroll
+      for (int a = 0; a < HW; ++a) {
+        const float sc = lane < nk ? s[a] * scale : -INFINITY;
+        const float m_new = fmaxf(m[a], warp_max(sc));           // finite: the tile holds at least one key
+        corr[a] = m[a] == -INFINITY ? 0.f : expf(m[a] - m_new);
+        const float pr = lane < nk ? expf(sc - m_new) : 0.f;
+        l[a] = fmaf(l[a], corr[a], warp_sum(pr));
+        m[a] = m_new;
+        p_s[(size_t)(warp * HW + a) * LT_KEYS + lane] = pr;
+      }
+      __syncwarp();
+      // weighted latent: this lane's columns of every row of the tile
+#pragma unroll
+      for (int a = 0; a < HW; ++a)
+#pragma unroll
+        for (int i = 0; i < RC; ++i) acc[a][i] *= corr[a];
+      for (int k = 0; k < nk; ++k) {
+        float cv[RC];
+#pragma unroll
+        for (int i = 0; i < RC; ++i) {
+          const int r = i * 32 + lane;
+          cv[i] = r < rank ? c_s[(size_t)k * RS + r] : 0.f;
+        }
+#pragma unroll
+        for (int a = 0; a < HW; ++a) {
+          const float pk = p_s[(size_t)(warp * HW + a) * LT_KEYS + k];
+#pragma unroll
+          for (int i = 0; i < RC; ++i) acc[a][i] = fmaf(pk, cv[i], acc[a][i]);
+        }
+      }
+      __syncwarp();
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < HW; ++a) {
+    const int h = h0 + a;
+    if (h >= H) continue;
+    float* out = parts + (((size_t)t * H + h) * n_slices + slice) * (rank + 2);   // an empty slice leaves (-inf, 0, zeros)
+    if (lane == 0) { out[0] = m[a]; out[1] = l[a]; }
+#pragma unroll
+    for (int i = 0; i < RC; ++i) {
+      const int r = i * 32 + lane;
+      if (r < rank) out[2 + r] = acc[a][i];
+    }
+  }
+}
+
+// lat [T, H, rank]: the slices of (token, head) brought together in slice order and divided by the softmax's sum
+__global__ void __launch_bounds__(128)
+latent_combine_kernel(const float* parts, const float* __restrict__ sink, float* lat, int H, int rank, int n_slices) {
+  pdl_launch_dependents();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* p = parts + ((size_t)t * H + h) * n_slices * (rank + 2);
+  const float sk = sink ? sink[h] : -INFINITY;
+  pdl_wait();
+  float M = sk;
+  for (int q = 0; q < n_slices; ++q) M = fmaxf(M, p[(size_t)q * (rank + 2)]);
+  float L = sink ? expf(sk - M) : 0.f;
+  for (int q = 0; q < n_slices; ++q) {
+    const float ms = p[(size_t)q * (rank + 2)];
+    L = fmaf(p[(size_t)q * (rank + 2) + 1], ms == -INFINITY ? 0.f : expf(ms - M), L);
+  }
+  const float inv = 1.0f / L;
+  float* dst = lat + ((size_t)t * H + h) * rank;
+  for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+    float a = 0.f;
+#pragma unroll 4
+    for (int q = 0; q < n_slices; ++q) {
+      const float ms = p[(size_t)q * (rank + 2)];
+      a = fmaf(p[(size_t)q * (rank + 2) + 2 + r], ms == -INFINITY ? 0.f : expf(ms - M), a);
+    }
+    dst[r] = a * inv;
+  }
+}
+
+constexpr int LPJ_COLS = 16;    // value columns of a block of `project` (two per warp)
+
+// out[t, h * dv + e] = Wv_h[e, :] . lat[t, h, :]
+template <typename T, int RC>
+__global__ void __launch_bounds__(256)
+latent_project_kernel(const float* lat, const T* __restrict__ w_v, T* out, int ldo, int n_tokens, int H, int dv,
+                      int rank) {
+  pdl_launch_dependents();
+  const int h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e0 = blockIdx.y * LPJ_COLS + warp * 2;
+  float w0[RC], w1[RC];
+#pragma unroll
+  for (int i = 0; i < RC; ++i) {
+    const int r = i * 32 + lane;
+    w0[i] = (e0 < dv && r < rank) ? to_float(w_v[((size_t)h * dv + e0) * rank + r]) : 0.f;
+    w1[i] = (e0 + 1 < dv && r < rank) ? to_float(w_v[((size_t)h * dv + e0 + 1) * rank + r]) : 0.f;
+  }
+  pdl_wait();
+  if (e0 >= dv) return;
+  for (int t = 0; t < n_tokens; ++t) {
+    const float* row = lat + ((size_t)t * H + h) * rank;
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < RC; ++i) {
+      const int r = i * 32 + lane;
+      const float v = r < rank ? row[r] : 0.f;
+      a0 = fmaf(w0[i], v, a0);
+      a1 = fmaf(w1[i], v, a1);
+    }
+    a0 = warp_sum(a0);
+    a1 = warp_sum(a1);
+    if (lane == 0) {
+      out[(size_t)t * ldo + h * dv + e0] = from_float<T>(a0);
+      if (e0 + 1 < dv) out[(size_t)t * ldo + h * dv + e0 + 1] = from_float<T>(a1);
+    }
+  }
+}
+
+inline bool latent_tiles_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("DLGO_LATENT_TILES");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+// register budget of the tile kernel: HW heads x RC columns of sums per lane
+inline int lt_heads_per_warp(int H) { return H <= 8 ? 1 : (H <= 16 ? 2 : (H <= 32 ? 4 : 0)); }
+inline int lt_columns(int rank) { return rank <= 128 ? 4 : (rank <= 256 ? 8 : (rank <= 640 ? 20 : (rank <= 1024 ? 32 : 0))); }
+inline size_t lt_smem_bytes(int H, int rank) {
+  return ((size_t)H * rank + (size_t)LT_KEYS * lt_row_stride(rank) + (size_t)LT_WARPS * 4 * LT_KEYS) * sizeof(float);
+}
+inline bool latent_tiles_takes(int elem_bytes, int H, int rank) {
+  const int v = 16 / elem_bytes;
+  const int hw = lt_heads_per_warp(H), rc = lt_columns(rank);
+  return latent_tiles_enabled() && hw > 0 && rc > 0 && hw * rc <= 80 && rank % v == 0 && rank % 4 == 0 &&
+         lt_smem_bytes(H, rank) <= 200 * 1024;
+}
+
+template <typename T, int RC, int HW>
+static int launch_latent_tile(const float* q_lat, const void* pages, const int* page_table, int max_pages, int page_size,
+                              const int* seq_slot, const int* token_seq, const int* token_pos, float* parts,
+                              int n_tokens, int H, int rank, int n_slices, float scale, int window,
+                              cudaStream_t stream) {
+  const size_t smem = lt_smem_bytes(H, rank);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(latent_tile_kernel<T, RC, HW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  launch_kernel(latent_tile_kernel<T, RC, HW>, dim3(n_tokens, n_slices), dim3(LT_WARPS * 32), smem, stream, q_lat,
+                (const T*)pages, page_table, max_pages, page_size, seq_slot, token_seq, token_pos, parts, H, rank,
+                n_slices, scale, window);
+  return launch_status();
+}
+
+template <typename T, int RC>
+static int launch_latent_tile_by_heads(const float* q_lat, const void* pages, const int* page_table, int max_pages,
+                                       int page_size, const int* seq_slot, const int* token_seq, const int* token_pos,
+                                       float* parts, int n_tokens, int H, int rank, int n_slices, float scale,
+                                       int window, cudaStream_t stream) {
+#define LT_ARGS q_lat, pages, page_table, max_pages, page_size, seq_slot, token_seq, token_pos, parts, n_tokens, H, rank, \
+                n_slices, scale, window, stream
+  const int hw = lt_heads_per_warp(H);
+  if (hw == 1) return launch_latent_tile<T, RC, 1>(LT_ARGS);
+  if (hw == 2) return launch_latent_tile<T, RC, 2>(LT_ARGS);
+  if (hw == 4 && RC <= 20) return launch_latent_tile<T, (RC <= 20 ? RC : 4), 4>(LT_ARGS);
+  return DLGO_ERR_SIZE;
+#undef LT_ARGS
+}
+
+// the four launches: queries into latent space (latent_absorb), tiles, combine, project
+template <typename T>
+static int launch_latent_tiles(const void* q, int q_is_f32, int ldq, const void* w_k, const void* w_v, const float* sink,
+                               const void* pages, const int* page_table, int max_pages, int page_size,
+                               const int* seq_slot, const int* token_seq, const int* token_pos, void* out, int ldo,
+                               int n_tokens, int H, int dk, int dv, int rank, float scale, int window, int n_slices,
+                               float* q_lat, float* parts, cudaStream_t stream) {
+  const size_t smem_a = (size_t)(AB_TOKENS * dk + 4 * AB_TOKENS * AB_COLS) * sizeof(float);
+  if (smem_a > 48 * 1024) return DLGO_ERR_SIZE;
+  launch_kernel(latent_absorb_kernel<T>, dim3(H, (rank + AB_COLS - 1) / AB_COLS, (n_tokens + AB_TOKENS - 1) / AB_TOKENS),
+                dim3(128), smem_a, stream, q, q_is_f32, ldq, (const T*)w_k, q_lat, n_tokens, H, dk, rank);
+  int st = launch_status();
+  if (st != DLGO_OK) return st;
+#define LT_ARGS q_lat, pages, page_table, max_pages, page_size, seq_slot, token_seq, token_pos, parts, n_tokens, H, rank, \
+                n_slices, scale, window, stream
+  const int rc = lt_columns(rank);
+  if (rc == 4) st = launch_latent_tile_by_heads<T, 4>(LT_ARGS);
+  else if (rc == 8) st = launch_latent_tile_by_heads<T, 8>(LT_ARGS);
+  else if (rc == 20) st = launch_latent_tile_by_heads<T, 20>(LT_ARGS);
+  else if (rc == 32) st = launch_latent_tile_by_heads<T, 32>(LT_ARGS);
+  else return DLGO_ERR_SIZE;
+#undef LT_ARGS
+  if (st != DLGO_OK) return st;
+  // the queries in latent space have been read: their place takes the weighted latents
+  launch_kernel(latent_combine_kernel, dim3(n_tokens, H), dim3(128), 0, stream, parts, sink, q_lat, H, rank, n_slices);
+  st = launch_status();
+  if (st != DLGO_OK) return st;
+  const dim3 grid(H, (dv + LPJ_COLS - 1) / LPJ_COLS);
+  if (rc == 4) launch_kernel(latent_project_kernel<T, 4>, grid, dim3(256), 0, stream, q_lat, (const T*)w_v, (T*)out, ldo, n_tokens, H, dv, rank);
+  else if (rc == 8) launch_kernel(latent_project_kernel<T, 8>, grid, dim3(256), 0, stream, q_lat, (const T*)w_v, (T*)out, ldo, n_tokens, H, dv, rank);
+  else if (rc == 20) launch_kernel(latent_project_kernel<T, 20>, grid, dim3(256), 0, stream, q_lat, (const T*)w_v, (T*)out, ldo, n_tokens, H, dv, rank);
+  else launch_kernel(latent_project_kernel<T, 32>, grid, dim3(256), 0, stream, q_lat, (const T*)w_v, (T*)out, ldo, n_tokens, H, dv, rank);
+  return launch_status();
+}
+
 template <typename T, int NP>
 static int launch_latent(const void* q, int q_is_f32, int ldq, const void* w_k, const void* w_v, const float* sink,
                          const void* pages, const int* page_table, int max_pages, int page_size, const int* seq_slot,
@@ -728,6 +1013,30 @@ DLGO_EXPORT int dlgo_latent_attention_few(const void* q, int q_is_f32, int ldq, 
     return latent_few_by_rank<__nv_bfloat16>(FEW_ARGS);
   }
   return DLGO_ERR_DTYPE;
+}
+
+// The same through tiles of keys that serve all heads (four launches); `takes` says whether the sizes fit.
+DLGO_EXPORT int dlgo_latent_attention_tiles_takes(int dtype, int H, int rank) {
+  if (dtype != DLGO_F32 && dtype != DLGO_BF16) return 0;
+  return latent_tiles_takes(dtype == DLGO_F32 ? 4 : 2, H, rank) ? 1 : 0;
+}
+
+DLGO_EXPORT int dlgo_latent_attention_tiles(const void* q, int q_is_f32, int ldq, const void* w_k, const void* w_v,
+                                            const float* sink, const void* pages, int dtype, const int* page_table,
+                                            int max_pages, int page_size, const int* seq_slot, const int* token_seq,
+                                            const int* token_pos, void* out, int ldo, int T_tokens, int H, int dk,
+                                            int dv, int rank, float scale, int window, int n_slices, float* q_lat,
+                                            float* parts, cudaStream_t stream) {
+  if (T_tokens <= 0) return DLGO_OK;
+  if (H <= 0 || dk <= 0 || dv <= 0 || rank <= 0 || page_size <= 0 || window < 0 || n_slices < 1 || n_slices > 65535 ||
+      H > 65535 || !dlgo_latent_attention_tiles_takes(dtype, H, rank))
+    return DLGO_ERR_SIZE;
+  if (((uintptr_t)pages & 15) || ((uintptr_t)q_lat & 15)) return DLGO_ERR_ALIGN;
+#define TILES_ARGS q, q_is_f32, ldq, w_k, w_v, sink, pages, page_table, max_pages, page_size, seq_slot, token_seq, \
+                   token_pos, out, ldo, T_tokens, H, dk, dv, rank, scale, window, n_slices, q_lat, parts, stream
+  if (dtype == DLGO_F32) return launch_latent_tiles<float>(TILES_ARGS);
+  return launch_latent_tiles<__nv_bfloat16>(TILES_ARGS);
+#undef TILES_ARGS
 }
 
 // q [T, >= H*dk] (fp32 or the cache's type), w_k [H*dk, rank], w_v [H*dv, rank], pages [n, page_size, rank],

@@ -42,6 +42,7 @@ PROMPT_TC_MIN_TOKENS = int(os.environ.get("DLGO_LATENT_TC_MIN_TOKENS", 64))
 
 FEW_TOKENS = 64      # steps of up to this many tokens run the three-launch kernels
 SLICE_BLOCKS_PER_SM = int(os.environ.get("DLGO_LATENT_SLICE_BLOCKS", 4))   # blocks of the softmax launch wanted per SM
+TILE_BLOCKS_PER_SM = int(os.environ.get("DLGO_LATENT_TILE_BLOCKS", 2))     # ... of the launch that serves all heads from one tile
 
 
 class LatentAttention(Mixer):
@@ -155,6 +156,20 @@ class LatentAttention(Mixer):
             self.wo(out, ADD_F32, residual)
             return
         T, H, R = ctx.n_tokens, self.n_heads, self.row
+        if T <= FEW_TOKENS and K.latent_attention_tiles_takes(cache.keys.dtype, H, R):
+            # decoding: a block per token and slice of its keys serves all heads from one tile of latents; slices
+            # so that the GPU has a couple of blocks per SM, of 32 keys or more each
+            longest = ctx.capacity if ctx.captured else ctx.max_len
+            span = min(longest, self.window) if self.window else longest
+            from .tensor_core import sm_count
+            n_slices = max(1, min((TILE_BLOCKS_PER_SM * sm_count(x.device)) // T, span // 32, 32))
+            out = K.latent_attention_tiles(q, self.w_k_up, self.w_v_up, self.sink, cache.keys, cache.page_table,
+                                           ctx.seq_slot, ctx.token_seq, ctx.token_pos, H, self.q_head, self.v_dim,
+                                           self.scale, self.window or 0, n_slices,
+                                           ctx.scratch("latent_q", T * H * R),
+                                           ctx.scratch("latent_parts", T * H * n_slices * (R + 2)))
+            self.wo(out, ADD_F32, residual)
+            return
         if T <= FEW_TOKENS and K.latent_attention_few_takes(cache.keys.dtype, R):
             # decoding: enough blocks for the whole GPU whatever the batch (a token's keys in slices of 64 or more)
             longest = ctx.capacity if ctx.captured else ctx.max_len
