@@ -596,10 +596,10 @@ static int launch_latent_few(const void* q, int q_is_f32, int ldq, const void* w
 // latents, which sit in shared memory and are read as broadcasts), for the weighted latent a lane owns RC columns
 // of the row (registers: HW x RC sums).  Online softmax per head in fp32.  Leaves (max, sum, weighted latent) per
 // (token, head, slice) in the format of latent_partial.  Then
-//   combine  a block per (token, head): the slices meet in slice order, the sink joins the denominator; leaves the
-//            normalised weighted latent (fp32)
-//   project  a block per (head, 16 value columns): two rows of Wv_h per warp in registers, every token's weighted
-//            latent read once per block
+//   combine  a block per (token, head): the slices meet in slice order (at most 32), the sink joins the
+//            denominator; leaves the normalised weighted latent (fp32)
+//   project  a block per (head, 16 value columns, 8 tokens): two rows of Wv_h per warp in registers, the weighted
+//            latents of several tokens fetched together
 constexpr int LT_KEYS = 32, LT_WARPS = 8;
 
 __host__ __device__ inline int lt_row_stride(int rank) { return rank + ((rank & 7) == 0 ? 4 : 8); }
@@ -626,8 +626,20 @@ latent_tile_kernel(const float* q_lat, const T* pages, const int* __restrict__ p
   const int j0 = lo + slice * per, j1 = min(pos + 1, j0 + per);
   const int h0 = warp * HW;
   pdl_wait();
-  for (int i = threadIdx.x * 4; i < H * rank; i += LT_WARPS * 32 * 4)
-    *reinterpret_cast<float4*>(q_s + i) = *reinterpret_cast<const float4*>(q_lat + (size_t)t * H * rank + i);
+  {
+    // (four fetches in flight per thread: one after another they would cost a memory latency each)
+    const float* qg = q_lat + (size_t)t * H * rank;
+    constexpr int STEP = LT_WARPS * 32 * 4;
+    for (int i0 = threadIdx.x * 4; i0 < H * rank; i0 += 4 * STEP) {
+      float4 tmp[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * STEP < H * rank) tmp[u] = *reinterpret_cast<const float4*>(qg + i0 + u * STEP);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * STEP < H * rank) *reinterpret_cast<float4*>(q_s + i0 + u * STEP) = tmp[u];
+    }
+  }
   float m[HW], l[HW], acc[HW][RC];
 #pragma unroll
   for (int a = 0; a < HW; ++a) {
@@ -640,20 +652,31 @@ latent_tile_kernel(const float* q_lat, const T* pages, const int* __restrict__ p
   for (int jt = j0; jt < j1; jt += LT_KEYS) {
     const int nk = min(LT_KEYS, j1 - jt);
     __syncthreads();                            // (the tile before has been read; q_s is complete)
-    for (int idx = threadIdx.x; idx < LT_KEYS * pieces; idx += LT_WARPS * 32) {
-      const int k = idx / pieces, piece = idx - k * pieces;
-      float v[V];
-      if (k < nk) {
-        const int j = jt + k;
-        const T* row = pages + ((size_t)table[j / page_size] * page_size + j % page_size) * rank;
-        Vec16<T>::load(row + piece * V, v);
-      } else {
+    for (int idx0 = threadIdx.x; idx0 < LT_KEYS * pieces; idx0 += 4 * LT_WARPS * 32) {
+      // four 16-byte pieces in flight per thread; a key beyond the slice's end gives zeros
+      uint4 raw[4];
 #pragma unroll
-        for (int e = 0; e < V; ++e) v[e] = 0.f;
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + u * LT_WARPS * 32;
+        const int k = idx / pieces, piece = idx - k * pieces;
+        raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (idx < LT_KEYS * pieces && k < nk) {
+          const int j = jt + k;
+          const T* row = pages + ((size_t)table[j / page_size] * page_size + j % page_size) * rank;
+          raw[u] = *reinterpret_cast<const uint4*>(row + piece * V);
+        }
       }
-      float* dst = c_s + (size_t)k * RS + piece * V;
 #pragma unroll
-      for (int e = 0; e < V; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + u * LT_WARPS * 32;
+        if (idx >= LT_KEYS * pieces) continue;
+        const int k = idx / pieces, piece = idx - k * pieces;
+        float v[V];
+        Vec16<T>::unpack(raw[u], v);
+        float* dst = c_s + (size_t)k * RS + piece * V;
+#pragma unroll
+        for (int e = 0; e < V; e += 4) *reinterpret_cast<float4*>(dst + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+      }
     }
     __syncthreads();
     if (h0 < H) {
@@ -722,43 +745,48 @@ latent_tile_kernel(const float* q_lat, const T* pages, const int* __restrict__ p
 }
 
 // lat [T, H, rank]: the slices of (token, head) brought together in slice order and divided by the softmax's sum
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 latent_combine_kernel(const float* parts, const float* __restrict__ sink, float* lat, int H, int rank, int n_slices) {
   pdl_launch_dependents();
   const int t = blockIdx.x, h = blockIdx.y;
   const float* p = parts + ((size_t)t * H + h) * n_slices * (rank + 2);
   const float sk = sink ? sink[h] : -INFINITY;
+  __shared__ float f_s[32];                   // a slice's factor: exp(its max - the common max) / the common sum
   pdl_wait();
-  float M = sk;
-  for (int q = 0; q < n_slices; ++q) M = fmaxf(M, p[(size_t)q * (rank + 2)]);
-  float L = sink ? expf(sk - M) : 0.f;
-  for (int q = 0; q < n_slices; ++q) {
-    const float ms = p[(size_t)q * (rank + 2)];
-    L = fmaf(p[(size_t)q * (rank + 2) + 1], ms == -INFINITY ? 0.f : expf(ms - M), L);
+  if (threadIdx.x < 32) {
+    // lane q holds slice q (at most 32 slices); the sum runs in slice order
+    const int lane = threadIdx.x;
+    const float ms = lane < n_slices ? p[(size_t)lane * (rank + 2)] : -INFINITY;
+    const float ls = lane < n_slices ? p[(size_t)lane * (rank + 2) + 1] : 0.f;
+    const float M = fmaxf(warp_max(ms), sk);
+    const float es = ms == -INFINITY ? 0.f : expf(ms - M);
+    float L = sink ? expf(sk - M) : 0.f;
+    for (int q = 0; q < n_slices; ++q) L = fmaf(__shfl_sync(0xffffffffu, ls, q), __shfl_sync(0xffffffffu, es, q), L);
+    f_s[lane] = es / L;
   }
-  const float inv = 1.0f / L;
+  __syncthreads();
   float* dst = lat + ((size_t)t * H + h) * rank;
   for (int r = threadIdx.x; r < rank; r += blockDim.x) {
     float a = 0.f;
-#pragma unroll 4
-    for (int q = 0; q < n_slices; ++q) {
-      const float ms = p[(size_t)q * (rank + 2)];
-      a = fmaf(p[(size_t)q * (rank + 2) + 2 + r], ms == -INFINITY ? 0.f : expf(ms - M), a);
-    }
-    dst[r] = a * inv;
+#pragma unroll 8
+    for (int q = 0; q < n_slices; ++q) a = fmaf(p[(size_t)q * (rank + 2) + 2 + r], f_s[q], a);
+    dst[r] = a;
   }
 }
 
 constexpr int LPJ_COLS = 16;    // value columns of a block of `project` (two per warp)
+constexpr int LPJ_TOKENS = 8;   // tokens of a block of `project`
 
-// out[t, h * dv + e] = Wv_h[e, :] . lat[t, h, :]
+// out[t, h * dv + e] = Wv_h[e, :] . lat[t, h, :]; the rows of TG tokens are fetched together
 template <typename T, int RC>
 __global__ void __launch_bounds__(256)
 latent_project_kernel(const float* lat, const T* __restrict__ w_v, T* out, int ldo, int n_tokens, int H, int dv,
                       int rank) {
+  constexpr int TG = RC <= 20 ? 4 : 2;
   pdl_launch_dependents();
   const int h = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int e0 = blockIdx.y * LPJ_COLS + warp * 2;
+  const int t_begin = blockIdx.z * LPJ_TOKENS, t_end = min(n_tokens, t_begin + LPJ_TOKENS);
   float w0[RC], w1[RC];
 #pragma unroll
   for (int i = 0; i < RC; ++i) {
@@ -768,21 +796,31 @@ latent_project_kernel(const float* lat, const T* __restrict__ w_v, T* out, int l
   }
   pdl_wait();
   if (e0 >= dv) return;
-  for (int t = 0; t < n_tokens; ++t) {
-    const float* row = lat + ((size_t)t * H + h) * rank;
-    float a0 = 0.f, a1 = 0.f;
+  for (int tb = t_begin; tb < t_end; tb += TG) {
+    float v[TG][RC];
 #pragma unroll
-    for (int i = 0; i < RC; ++i) {
-      const int r = i * 32 + lane;
-      const float v = r < rank ? row[r] : 0.f;
-      a0 = fmaf(w0[i], v, a0);
-      a1 = fmaf(w1[i], v, a1);
+    for (int g = 0; g < TG; ++g) {
+      const float* row = lat + ((size_t)min(tb + g, t_end - 1) * H + h) * rank;
+#pragma unroll
+      for (int i = 0; i < RC; ++i) {
+        const int r = i * 32 + lane;
+        v[g][i] = r < rank ? row[r] : 0.f;
+      }
     }
-    a0 = warp_sum(a0);
-    a1 = warp_sum(a1);
-    if (lane == 0) {
-      out[(size_t)t * ldo + h * dv + e0] = from_float<T>(a0);
-      if (e0 + 1 < dv) out[(size_t)t * ldo + h * dv + e0 + 1] = from_float<T>(a1);
+#pragma unroll
+    for (int g = 0; g < TG; ++g) {
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < RC; ++i) {
+        a0 = fmaf(w0[i], v[g][i], a0);
+        a1 = fmaf(w1[i], v[g][i], a1);
+      }
+      a0 = warp_sum(a0);
+      a1 = warp_sum(a1);
+      if (lane == 0 && tb + g < t_end) {
+        out[(size_t)(tb + g) * ldo + h * dv + e0] = from_float<T>(a0);
+        if (e0 + 1 < dv) out[(size_t)(tb + g) * ldo + h * dv + e0 + 1] = from_float<T>(a1);
+      }
     }
   }
 }
@@ -862,10 +900,11 @@ static int launch_latent_tiles(const void* q, int q_is_f32, int ldq, const void*
 #undef LT_ARGS
   if (st != DLGO_OK) return st;
   // the queries in latent space have been read: their place takes the weighted latents
-  launch_kernel(latent_combine_kernel, dim3(n_tokens, H), dim3(128), 0, stream, parts, sink, q_lat, H, rank, n_slices);
+  launch_kernel(latent_combine_kernel, dim3(n_tokens, H), dim3(rank > 256 ? 512 : (rank > 128 ? 256 : 128)), 0, stream,
+                parts, sink, q_lat, H, rank, n_slices);
   st = launch_status();
   if (st != DLGO_OK) return st;
-  const dim3 grid(H, (dv + LPJ_COLS - 1) / LPJ_COLS);
+  const dim3 grid(H, (dv + LPJ_COLS - 1) / LPJ_COLS, (n_tokens + LPJ_TOKENS - 1) / LPJ_TOKENS);
   if (rc == 4) launch_kernel(latent_project_kernel<T, 4>, grid, dim3(256), 0, stream, q_lat, (const T*)w_v, (T*)out, ldo, n_tokens, H, dv, rank);
   else if (rc == 8) launch_kernel(latent_project_kernel<T, 8>, grid, dim3(256), 0, stream, q_lat, (const T*)w_v, (T*)out, ldo, n_tokens, H, dv, rank);
   else if (rc == 20) launch_kernel(latent_project_kernel<T, 20>, grid, dim3(256), 0, stream, q_lat, (const T*)w_v, (T*)out, ldo, n_tokens, H, dv, rank);
@@ -1028,7 +1067,7 @@ DLGO_EXPORT int dlgo_latent_attention_tiles(const void* q, int q_is_f32, int ldq
                                             int dv, int rank, float scale, int window, int n_slices, float* q_lat,
                                             float* parts, cudaStream_t stream) {
   if (T_tokens <= 0) return DLGO_OK;
-  if (H <= 0 || dk <= 0 || dv <= 0 || rank <= 0 || page_size <= 0 || window < 0 || n_slices < 1 || n_slices > 65535 ||
+  if (H <= 0 || dk <= 0 || dv <= 0 || rank <= 0 || page_size <= 0 || window < 0 || n_slices < 1 || n_slices > 32 ||
       H > 65535 || !dlgo_latent_attention_tiles_takes(dtype, H, rank))
     return DLGO_ERR_SIZE;
   if (((uintptr_t)pages & 15) || ((uintptr_t)q_lat & 15)) return DLGO_ERR_ALIGN;
