@@ -602,6 +602,8 @@ static int launch_latent_few(const void* q, int q_is_f32, int ldq, const void* w
 //            latents of several tokens fetched together
 constexpr int LT_KEYS = 32, LT_WARPS = 8;
 
+// Row stride of the key tile in floats: a multiple of 4 and odd in 16-byte units, so that a lane per row reads
+// 16-byte pieces without bank conflicts.
 __host__ __device__ inline int lt_row_stride(int rank) { return rank + ((rank & 7) == 0 ? 4 : 8); }
 
 template <typename T, int RC, int HW>
@@ -684,18 +686,27 @@ latent_tile_kernel(const float* q_lat, const T* pages, const int* __restrict__ p
       float s[HW];
 #pragma unroll
       for (int a = 0; a < HW; ++a) s[a] = 0.f;
-      const float* crow = c_s + (size_t)lane * RS;
-      for (int r = 0; r < rank; r += 4) {
-        const float4 cv = *reinterpret_cast<const float4*>(crow + r);
+      const float4* crow = reinterpret_cast<const float4*>(c_s + (size_t)lane * RS);
+      const float4* qrow[HW];
+#pragma unroll
+      for (int a = 0; a < HW; ++a) qrow[a] = reinterpret_cast<const float4*>(q_s + (size_t)min(h0 + a, H - 1) * rank);
+      float s2[HW];                                  // (two chains per head)
+#pragma unroll
+      for (int a = 0; a < HW; ++a) s2[a] = 0.f;
+#pragma unroll 4
+      for (int r4 = 0; r4 < (rank >> 2); ++r4) {
+        const float4 cv = crow[r4];
 #pragma unroll
         for (int a = 0; a < HW; ++a) {
-          const float4 qv = *reinterpret_cast<const float4*>(q_s + (size_t)min(h0 + a, H - 1) * rank + r);
+          const float4 qv = qrow[a][r4];
           s[a] = fmaf(qv.x, cv.x, s[a]);
-          s[a] = fmaf(qv.y, cv.y, s[a]);
+          s2[a] = fmaf(qv.y, cv.y, s2[a]);
           s[a] = fmaf(qv.z, cv.z, s[a]);
-          s[a] = fmaf(qv.w, cv.w, s[a]);
+          s2[a] = fmaf(qv.w, cv.w, s2[a]);
         }
       }
+#pragma unroll
+      for (int a = 0; a < HW; ++a) s[a] += s2[a];
       float corr[HW];
 #pragma unroll
       for (int a = 0; a < HW; ++a) {
@@ -713,16 +724,17 @@ latent_tile_kernel(const float* q_lat, const T* pages, const int* __restrict__ p
       for (int a = 0; a < HW; ++a)
 #pragma unroll
         for (int i = 0; i < RC; ++i) acc[a][i] *= corr[a];
-      for (int k = 0; k < nk; ++k) {
+      const float* ck = c_s + lane;
+      const float* pw = p_s + (size_t)warp * HW * LT_KEYS;
+#pragma unroll 2
+      for (int k = 0; k < nk; ++k, ck += RS) {
         float cv[RC];
 #pragma unroll
-        for (int i = 0; i < RC; ++i) {
-          const int r = i * 32 + lane;
-          cv[i] = r < rank ? c_s[(size_t)k * RS + r] : 0.f;
-        }
+        for (int i = 0; i < RC; ++i) cv[i] = ck[i * 32];          // (columns beyond the rank read on into the next row,
+                                                                  // or behind the tile into p_s: sums that are never stored)
 #pragma unroll
         for (int a = 0; a < HW; ++a) {
-          const float pk = p_s[(size_t)(warp * HW + a) * LT_KEYS + k];
+          const float pk = pw[a * LT_KEYS + k];
 #pragma unroll
           for (int i = 0; i < RC; ++i) acc[a][i] = fmaf(pk, cv[i], acc[a][i]);
         }
@@ -838,6 +850,7 @@ inline bool latent_tiles_enabled() {
 inline int lt_heads_per_warp(int H) { return H <= 8 ? 1 : (H <= 16 ? 2 : (H <= 32 ? 4 : 0)); }
 inline int lt_columns(int rank) { return rank <= 128 ? 4 : (rank <= 256 ? 8 : (rank <= 640 ? 20 : (rank <= 1024 ? 32 : 0))); }
 inline size_t lt_smem_bytes(int H, int rank) {
+  // (the probabilities' rows come last, 1,024 floats: reads of columns beyond the rank run less than that past the tile)
   return ((size_t)H * rank + (size_t)LT_KEYS * lt_row_stride(rank) + (size_t)LT_WARPS * 4 * LT_KEYS) * sizeof(float);
 }
 inline bool latent_tiles_takes(int elem_bytes, int H, int rank) {
