@@ -561,3 +561,53 @@ def test_trace_replay_command(dirs, tmp_path):
     for i, ref in want.items():
         got = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V))
         assert_rows(got, ref, "float32", f"step {i}")
+
+
+# ------------------------------------------------- latent attention for few tokens: tiles of keys that serve all heads
+@pytest.mark.parametrize("act_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, dk, dv, rank, window, sink", [(16, 24, 20, 48, 0, False), (1, 8, 40, 16, 0, True), (3, 16, 8, 136, 70, False),
+                                                           (8, 32, 32, 128, 0, False), (24, 16, 24, 264, 33, True), (32, 8, 16, 576, 0, False),
+                                                           (9, 12, 10, 648, 0, False)])
+def test_latent_attention_from_tiles_of_keys(H, dk, dv, rank, window, sink, act_dtype):
+    """Tokens of several sequences at positions around page and tile borders, keys in slices of unequal sizes (some
+    empty): scores, softmax (with a window and a sink) and the way out against their formulas."""
+    from dlgo_b200.csrc import kernels as K
+    assert K.latent_attention_tiles_takes(act_dtype, H, rank)
+    g = torch.Generator().manual_seed(H + rank)
+    PS = 64
+    lens = [1, 31, 32, 33, 64, 65, 200, 129]                      # the token of sequence i sits at position lens[i] - 1
+    n_pages = sum(-(-n // PS) for n in lens)
+    pages = (torch.randn(n_pages, PS, rank, generator=g) * 0.7).to(act_dtype)
+    order = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((len(lens), 4), -1, dtype=torch.int32)
+    at = 0
+    for i, n in enumerate(lens):
+        for p in range(-(-n // PS)):
+            table[i, p] = order[at]
+            at += 1
+    wk = (torch.randn(H * dk, rank, generator=g) / rank ** 0.5).to(act_dtype)
+    wv = (torch.randn(H * dv, rank, generator=g) / rank ** 0.5).to(act_dtype)
+    q = torch.randn(len(lens), H * dk + 5, generator=g) * 2.0
+    sk = torch.randn(H, generator=g) if sink else None
+    scale = 0.3
+    T = len(lens)
+    for n_slices in (1, 3, 7):
+        out = K.latent_attention_tiles(q.to(DEV)[:, :H * dk], wk.to(DEV), wv.to(DEV), None if sk is None else sk.to(DEV),
+                                       pages.to(DEV), table.to(DEV), i32(list(range(T))), i32(list(range(T))),
+                                       i32([n - 1 for n in lens]), H, dk, dv, scale, window, n_slices,
+                                       torch.empty(T * H * rank, device=DEV),
+                                       torch.empty(T * H * n_slices * (rank + 2), device=DEV)).float().cpu().double()
+        for i, n in enumerate(lens):
+            rows = torch.cat([pages[int(table[i, p])] for p in range(-(-n // PS))]).double()[:n]
+            if window:
+                rows = rows[max(0, n - window):]
+            for h in range(H):
+                ql = wk.double()[h * dk:(h + 1) * dk].T @ q[i, h * dk:(h + 1) * dk].double()
+                s = rows @ ql * scale
+                if sk is not None:
+                    s = torch.cat([s, sk[h:h + 1].double()])
+                pr = torch.softmax(s, 0)[:rows.shape[0]]
+                want = wv.double()[h * dv:(h + 1) * dv] @ (pr @ rows)
+                tol = 3e-2 if act_dtype == torch.bfloat16 else 1e-4
+                assert torch.allclose(out[i, h * dv:(h + 1) * dv], want, rtol=tol, atol=tol * float(want.abs().max())), \
+                    (n_slices, i, h, float((out[i, h * dv:(h + 1) * dv] - want).abs().max()))
