@@ -101,7 +101,7 @@ class RagilornMixer:
     scale: float
     rot: Optional[Rotation]
     kv_heads: int = 1           # attention
-    conv: int = 1               # attention: taps of the convolution over time (1: none)
+    conv: Optional[int] = None  # attention: taps of the convolution over time (None: no convolution)
     chunk: Optional[int] = None  # attention: mask.size
     kv_rank: int = 0            # latent attention
     rot_dim: int = 0            # latent attention: size of the rotated part
@@ -137,8 +137,8 @@ class RagilornConfig:
             kv = _opt(m, "kv_heads", int, heads)
             if kv <= 0 or heads % kv:
                 raise ConfigError(f"config.json: {where}kv_heads ({kv}) must divide heads ({heads})")
-            conv = _opt(m, "conv", int, 1) or 1
-            if conv < 1:
+            conv = _opt(m, "conv", int, None) or None       # (absent, null or 0: no convolution)
+            if conv is not None and conv < 1:
                 raise ConfigError(f"config.json: {where}conv must be at least 1, got {conv}")
             chunk = None
             if m.get("mask") is not None:
@@ -204,7 +204,7 @@ class RagilornConfig:
                 mixer["rot"] = m.rot.to_dict()
             if m.kind == "attention":
                 mixer["kv_heads"] = m.kv_heads
-                if m.conv > 1:
+                if m.conv is not None:
                     mixer["conv"] = m.conv
                 if m.chunk is not None:
                     mixer["mask"] = {"size": m.chunk}

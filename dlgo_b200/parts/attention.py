@@ -481,7 +481,7 @@ class ShortConvAttention(GQAAttention):
             raise ValueError("a window or chunks, not both")
         if chunk is not None and chunk <= 0:
             raise ValueError(f"chunk must be positive or None, got {chunk}")
-        taps = int(conv_taps or 1)
+        taps = int(conv_taps or 1)          # (None: no convolution and no taps in the file; 1: one tap per channel)
         if not 1 <= taps <= K.CONV_MAX_TAPS:
             raise ValueError(f"conv_taps must be 1 to {K.CONV_MAX_TAPS}, got {conv_taps}")
         padded = -(-max(self.qk_dim, self.v_dim) // self.head_multiple) * self.head_multiple
@@ -492,6 +492,7 @@ class ShortConvAttention(GQAAttention):
         self.chunk = None if chunk is None else int(chunk)
         self.bias = bool(bias)
         self.taps = taps
+        self.has_conv = conv_taps is not None and int(conv_taps) >= 1
         self.channels = (self.num_heads + self.num_kv_heads) * self.qk_dim + self.num_kv_heads * self.v_dim
         self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "out": "o_proj.weight",
                       "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
@@ -513,7 +514,7 @@ class ShortConvAttention(GQAAttention):
             for key, rows in sizes.items():
                 specs[n[key + "_bias"]] = ParamSpec((rows,))
             specs[n["out_bias"]] = ParamSpec((d,))
-        if self.taps > 1:
+        if self.has_conv:
             for key, rows in sizes.items():
                 specs[n[key + "_conv"]] = ParamSpec((rows, self.taps), "last_one_plus_normal")
         return specs
@@ -537,7 +538,7 @@ class ShortConvAttention(GQAAttention):
         if self.bias:       # added in fp32: to the projection's fp32 result, and to the fp32 sum the mixer adds into
             self.b_in = torch.cat([get(n[key + "_bias"]).to(torch.float32) for key in ("q", "k", "v")]).contiguous()
             self.output_bias = get(n["out_bias"]).to(torch.float32).contiguous()
-        if self.taps > 1:
+        if self.has_conv:
             self.w_taps = torch.cat([get(n[key + "_conv"]).to(torch.float32) for key in ("q", "k", "v")],
                                     dim=0).contiguous()
 

@@ -45,7 +45,7 @@ def test_parts_carry_the_file_s_constants():
     assert l0.ffn.params["score"] == "sigmoid" and not l0.ffn.params["renormalize"] and l0.ffn.params["gated"]
     assert l1.mixer.kind == "short_conv_attention" and l1.mixer.params["conv_taps"] == 3 and l1.mixer.params["chunk"] == 37
     assert l1.ffn is None and set(l1.norms) == {"mixer_norm"} and "ffn_gate" not in l1.connections
-    assert l2.mixer.params["chunk"] is None and l2.mixer.params["conv_taps"] == 1
+    assert l2.mixer.params["chunk"] is None and l2.mixer.params["conv_taps"] is None
     assert [l.connections["depth_average"].params["depth"] for l in spec.layers] == [2, 3, 4, 5]
     assert all(l.connections["depth_average"].params["total"] == 5 for l in spec.layers)
     # every distinct rotation is a position encoding of its own; neighbouring pairs; YaRN where the file has it

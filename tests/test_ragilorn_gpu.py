@@ -274,6 +274,18 @@ def test_attention_alone(H, G, dk, dv, rot, conv, chunk, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_sizes_off_every_grid(dtype):
+    """A width, a vocabulary and head sizes that are no multiple of 8 (contractions on the fp32 pipes also in bfloat16,
+    the plain forms of the row kernels), a convolution of one tap, experts of an odd width."""
+    cfg = model(61, 100, [layer(att(5, 5, 12, 18, 0.3, 6, 900.0, yarn(2.0, 20), conv=1, chunk=50), moe(30, 3, 2)),
+                          layer(lat(3, 10, 6, 14, 22, 0.3, 500.0), dense(52)),
+                          layer(att(2, 1, 7, 5, 0.4, 4, 70.0, None, conv=3), None)], eps=1e-6, emb=1.3, logit_scale=1.5, softcap=3.0)
+    w = make_weights(cfg, 23, mild=(dtype == "bfloat16"))
+    assert w["l0.mix.q.conv"].shape == (60, 1)
+    check_model(cfg, w, dtype, "sizes off every grid", n=130, start=55)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H, dk, r, dv, R", [(3, 24, 8, 20, 40), (1, 8, 4, 40, 9), (4, 32, 32, 64, 96), (2, 64, 64, 128, 128),
                                              (6, 64, 16, 72, 112), (2, 16, 16, 24, 18), (2, 96, 32, 128, 160)])
 def test_latent_attention_alone(H, dk, r, dv, R, dtype):
