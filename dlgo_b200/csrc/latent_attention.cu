@@ -846,7 +846,7 @@ inline bool latent_tiles_enabled() {
   return on == 1;
 }
 
-// register budget of the tile kernel: HW heads x RC columns of sums per lane
+// what the tile kernel keeps in registers: HW heads x RC columns of sums per lane
 inline int lt_heads_per_warp(int H) { return H <= 8 ? 1 : (H <= 16 ? 2 : (H <= 32 ? 4 : 0)); }
 inline int lt_columns(int rank) { return rank <= 128 ? 4 : (rank <= 256 ? 8 : (rank <= 640 ? 20 : (rank <= 1024 ? 32 : 0))); }
 inline size_t lt_smem_bytes(int H, int rank) {
